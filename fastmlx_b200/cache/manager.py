@@ -9,7 +9,8 @@ Pages, block tables and what happens when pages run out are this engine's own.
 Schedule entries whose mixers ask for the same (kv heads, head size, window) form a
 group with one pool, one page geometry and one block table per request; a group with a
 window gives a page back as soon as every position on it is out of every later query's
-reach.  Memory of a layer: [num_pages, 2 (k|v), kv_heads, page_size, head_dim].
+reach.  Memory of a layer: [num_pages, 2 (k|v), kv_heads, page_size, head_dim]; where values are
+of another width than keys, [num_pages, kv_heads * page_size * (head_dim + v_head_dim)], keys first.
 """
 from __future__ import annotations
 
@@ -30,7 +31,8 @@ class CacheGroup:
     kv: torch.Tensor | None = None      # [len(entries), num_pages, 2, nkv, page_size, hd]
 
     def page_bytes(self, elem: int) -> int:
-        return 2 * self.spec.num_kv_heads * self.pool.page_size * self.spec.head_dim * elem * len(self.entries)
+        return self.spec.num_kv_heads * self.pool.page_size * (self.spec.head_dim + self.spec.value_dim) * elem \
+            * len(self.entries)
 
 
 @dataclass
@@ -79,8 +81,11 @@ class CacheManager:
             self.groups[g].entries.append(pos)
         if allocate:
             for g in self.groups:
-                g.kv = torch.empty((len(g.entries), g.pool.num_pages, 2, g.spec.num_kv_heads,
-                                    page_size, g.spec.head_dim), dtype=dtype, device=device)
+                if g.spec.value_dim == g.spec.head_dim:
+                    shape = (2, g.spec.num_kv_heads, page_size, g.spec.head_dim)
+                else:           # keys, then values of another width: a page is one run of elements
+                    shape = (g.spec.num_kv_heads * page_size * (g.spec.head_dim + g.spec.value_dim),)
+                g.kv = torch.empty((len(g.entries), g.pool.num_pages, *shape), dtype=dtype, device=device)
         self.entries: list[EntryCache] = []
         for pos, (kv, state, src) in enumerate(cache_needs):
             st = None
@@ -113,7 +118,7 @@ class CacheManager:
         total = 0
         for g in self.groups:
             n = req.length if g.spec.window <= 0 else min(req.length, g.spec.window)
-            total += 2 * g.spec.num_kv_heads * g.spec.head_dim * e * len(g.entries) * n
+            total += g.spec.num_kv_heads * (g.spec.head_dim + g.spec.value_dim) * e * len(g.entries) * n
         return total
 
     @property

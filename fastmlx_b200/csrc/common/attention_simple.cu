@@ -8,6 +8,12 @@
 // maximum and sum, and the output accumulator are 32-bit.  The order of every sum depends
 // only on the key's position, never on how the tokens were cut into steps or on what else
 // is in the batch.
+//
+// The general entry takes queries of their own type (32-bit queries over a bfloat16 cache),
+// keys and values of different head sizes, and a cap on the scores: s <- cap * tanh(s / cap)
+// before the softmax.  A page holds its keys [nkv, page_size, hd] and then its values
+// [nkv, page_size, vd]; with hd = vd that is the layout [2, nkv, page_size, hd] of the other
+// attention kernels.  The output's rows may be wider than nh * vd (a slice of a joined buffer).
 #include <math.h>
 #include "common.cuh"
 
@@ -15,13 +21,13 @@ namespace {
 constexpr int WARPS = 4;
 constexpr int MAX_HD = 256;
 
-template <typename T>
+template <typename TQ, typename T>
 __global__ void __launch_bounds__(WARPS * 32)
-paged_attention_simple_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ kv,
+paged_attention_simple_kernel(const TQ* __restrict__ q, long long q_stride, const T* __restrict__ kv,
                               const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ token_row,
-                              const int* __restrict__ positions, T* __restrict__ out, int n_tokens, int nh, int nkv,
-                              int hd, int page_size, long long num_pages, float scale, int window, int R,
-                              int* status) {
+                              const int* __restrict__ positions, T* __restrict__ out, long long out_stride, int n_tokens,
+                              int nh, int nkv, int hd, int vd, int page_size, long long num_pages, float scale,
+                              float softcap, int window, int R, int* status) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * WARPS + warp;
@@ -29,21 +35,23 @@ paged_attention_simple_kernel(const T* __restrict__ q, long long q_stride, const
   const int t = (int)(w / nh), h = (int)(w - (long long)t * nh);
   const int g = h / (nh / nkv);
   float* qs = smem + warp * hd;
-  const T* qp = q + (long long)t * q_stride + (long long)h * hd;
+  const TQ* qp = q + (long long)t * q_stride + (long long)h * hd;
   for (int e = lane; e < hd; e += 32) qs[e] = to_f(qp[e]);
   __syncwarp();
 
   const int row = token_row[t];
-  T* op = out + ((long long)t * nh + h) * hd;
+  T* op = out + (long long)t * out_stride + (long long)h * vd;
   if (row < 0 || row >= R) {
     if (lane == 0) fmx_set_status(status, FMX_BAD_ROW, row, t);
-    for (int e = lane; e < hd; e += 32) op[e] = from_f<T>(0.f);
+    for (int e = lane; e < vd; e += 32) op[e] = from_f<T>(0.f);
     return;
   }
   const int pos = positions[t];
   const int* bt = block_tables + (long long)row * bt_stride;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const long long plane = (long long)nkv * page_size * hd;     // k plane -> v plane of a page
+  const long long plane = (long long)nkv * page_size * hd;     // a page's keys, then its values
+  const long long page_elems = (long long)nkv * page_size * (hd + vd);
+  const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
 
   float m = -INFINITY, l = 0.f;
   float acc[MAX_HD / 32];
@@ -62,11 +70,13 @@ paged_attention_simple_kernel(const T* __restrict__ q, long long q_stride, const
         fmx_set_status(status, FMX_BAD_PAGE, page, t);
         valid = false;
       } else {
-        const long long kbase = ((((long long)page * 2) * nkv + g) * page_size + (j - blk * page_size)) * hd;
-        vbase = kbase + plane;
+        const long long at = (long long)g * page_size + (j - blk * page_size);
+        const long long kbase = (long long)page * page_elems + at * hd;
+        vbase = (long long)page * page_elems + plane + at * vd;
         float dot = 0.f;
         for (int e = 0; e < hd; ++e) dot = fmaf(qs[e], to_f(kv[kbase + e]), dot);
         s = dot * scale;
+        if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -83,7 +93,7 @@ paged_attention_simple_kernel(const T* __restrict__ q, long long q_stride, const
 #pragma unroll
       for (int i = 0; i < MAX_HD / 32; ++i) {
         const int e = lane + 32 * i;
-        if (e < hd) acc[i] = fmaf(pj, to_f(kv[vb + e]), acc[i]);
+        if (e < vd) acc[i] = fmaf(pj, to_f(kv[vb + e]), acc[i]);
       }
     }
     m = m_new;
@@ -92,35 +102,52 @@ paged_attention_simple_kernel(const T* __restrict__ q, long long q_stride, const
 #pragma unroll
   for (int i = 0; i < MAX_HD / 32; ++i) {
     const int e = lane + 32 * i;
-    if (e < hd) op[e] = from_f<T>(acc[i] * inv);
+    if (e < vd) op[e] = from_f<T>(acc[i] * inv);
   }
 }
 }  // namespace
+
+// q_dtype: the queries' type (FMX_F32 beside a bfloat16 cache, or the cache's own); dtype: the type of the
+// cache and of the output; hd / vd: head sizes of keys and values; softcap <= 0: scores are not capped.
+FMX_EXPORT int fmx_paged_attention_general(const void* q, long long q_stride, int q_dtype, const void* kv,
+                                           const int* block_tables, int bt_stride, const int* token_row,
+                                           const int* positions, void* out, long long out_stride, int n_tokens, int nh,
+                                           int nkv, int hd, int vd, int page_size, long long num_pages, float scale,
+                                           float softcap, int window, int R, int dtype, int* status,
+                                           cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || vd <= 0 || page_size <= 0)
+    return fmx_fail("fmx_paged_attention_general: bad sizes T=%d nh=%d nkv=%d hd=%d vd=%d page=%d", n_tokens, nh, nkv, hd,
+                    vd, page_size);
+  if (hd > MAX_HD || vd > MAX_HD) return fmx_fail("fmx_paged_attention_general: head sizes %d / %d are above %d", hd, vd, MAX_HD);
+  if (out_stride < (long long)nh * vd) return fmx_fail("fmx_paged_attention_general: output rows too narrow");
+  const long long warps = (long long)n_tokens * nh;
+  const long long grid = (warps + WARPS - 1) / WARPS;
+  if (grid > 2147483647LL) return fmx_fail("fmx_paged_attention_general: batch too large");
+  const size_t smem = (size_t)WARPS * hd * sizeof(float);
+#define FMX_ATTN_SIMPLE(TQ, T)                                                                                        \
+  paged_attention_simple_kernel<TQ, T><<<(unsigned)grid, WARPS * 32, smem, stream>>>(                                 \
+      (const TQ*)q, q_stride, (const T*)kv, block_tables, bt_stride, token_row, positions, (T*)out, out_stride, n_tokens, \
+      nh, nkv, hd, vd, page_size, num_pages, scale, softcap, window, R, status)
+  if (dtype == FMX_F32 && q_dtype == FMX_F32)
+    FMX_ATTN_SIMPLE(float, float);
+  else if (dtype == FMX_BF16 && q_dtype == FMX_BF16)
+    FMX_ATTN_SIMPLE(bf16, bf16);
+  else if (dtype == FMX_BF16 && q_dtype == FMX_F32)
+    FMX_ATTN_SIMPLE(float, bf16);
+  else
+    return fmx_fail("fmx_paged_attention_general: no kernel for queries of type %d over a cache of type %d", q_dtype, dtype);
+#undef FMX_ATTN_SIMPLE
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
 
 FMX_EXPORT int fmx_paged_attention_simple(const void* q, long long q_stride, const void* kv, const int* block_tables,
                                           int bt_stride, const int* token_row, const int* positions, void* out,
                                           int n_tokens, int nh, int nkv, int hd, int page_size, long long num_pages,
                                           float scale, int window, int R, int dtype, int* status,
                                           cudaStream_t stream) {
-  if (n_tokens == 0) return 0;
-  if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || page_size <= 0)
-    return fmx_fail("fmx_paged_attention_simple: bad sizes T=%d nh=%d nkv=%d hd=%d page=%d", n_tokens, nh, nkv, hd,
-                    page_size);
-  if (hd > MAX_HD) return fmx_fail("fmx_paged_attention_simple: head size %d is above %d", hd, MAX_HD);
-  const long long warps = (long long)n_tokens * nh;
-  const long long grid = (warps + WARPS - 1) / WARPS;
-  if (grid > 2147483647LL) return fmx_fail("fmx_paged_attention_simple: batch too large");
-  const size_t smem = (size_t)WARPS * hd * sizeof(float);
-  if (dtype == FMX_F32)
-    paged_attention_simple_kernel<float><<<(unsigned)grid, WARPS * 32, smem, stream>>>(
-        (const float*)q, q_stride, (const float*)kv, block_tables, bt_stride, token_row, positions, (float*)out,
-        n_tokens, nh, nkv, hd, page_size, num_pages, scale, window, R, status);
-  else if (dtype == FMX_BF16)
-    paged_attention_simple_kernel<bf16><<<(unsigned)grid, WARPS * 32, smem, stream>>>(
-        (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, token_row, positions, (bf16*)out, n_tokens,
-        nh, nkv, hd, page_size, num_pages, scale, window, R, status);
-  else
-    return fmx_fail("fmx_paged_attention_simple: unknown dtype %d", dtype);
-  FMX_LAUNCH_CHECK();
-  return 0;
+  return fmx_paged_attention_general(q, q_stride, dtype, kv, block_tables, bt_stride, token_row, positions, out,
+                                     (long long)nh * hd, n_tokens, nh, nkv, hd, hd, page_size, num_pages, scale, 0.f,
+                                     window, R, dtype, status, stream);
 }

@@ -1,0 +1,284 @@
+// The gated delta rule: a linear-attention mixer whose per-request state is a matrix per head.
+//
+// Per head, with key k, query q (size D), value v (size Dv), decay g in (0, 1) and write strength
+// beta in (0, 1), a token does, in this order,
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q,
+// so the read-out sees the token's own write.  S [D, Dv] lives in 32-bit in a state slot of the
+// request and is carried from step to step; so are the last taps-1 inputs of the short causal
+// convolutions that q, k and v pass through.
+//
+// Four kernels:
+//   delta_prepare     per token: convolution + SiLU of the projected q | k | v channels (inputs before the
+//                     portion's start come from the slot's convolution state), q and k made unit vectors per head
+//                     (q also times D^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)).
+//   conv_state_update per request: the last taps-1 inputs of the portion replace the convolution state.
+//   delta_rule        the recurrence.  Columns of S are independent (column j needs v_j only), so a column is
+//                     given to 8 adjacent lanes that hold D/8 of its values each in registers; the tokens of a
+//                     request's portion are walked in order, the next token's operands loaded a token ahead.
+//   gated_rmsnorm     o of each head divided by its root mean square, times a weight, times SiLU(gate).
+//
+// A slot's state is one run of 32-bit floats: S^T of every head, [H, Dv, D], and then the convolution inputs,
+// [taps-1, C].  Everything is 32-bit but the projections that come in and the activations that go out.  No sum's
+// order depends on how a request's tokens were cut into steps or on what else is in the batch.
+#include <math.h>
+#include "common.cuh"
+
+namespace {
+constexpr int MAX_TAPS = 16;
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+// proj [T, stride]: q (G*D) | k (G*D) | v (H*Dv) | ... ; ab [T, ab_stride] 32-bit: b (H) | a (H).
+// out_qkv [T, C] 32-bit; out_gb [T, 2H]: decay | beta.
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(const T* proj, long long stride, const float* ab, long long ab_stride,
+                     const float* __restrict__ conv_w, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                     const int* token_row, const int* row_start, const int* row_slot, const float* state,
+                     long long slot_stride, long long conv_off, float* out_qkv, float* out_gb, int H, int G, int D,
+                     int Dv, int taps, int R, int max_slots, int* status) {
+  extern __shared__ float vals[];               // the token's C channels after convolution and SiLU
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int C = 2 * G * D + H * Dv;
+  const int r = token_row[t];
+  float* oq = out_qkv + (long long)t * C;
+  float* og = out_gb + (long long)t * 2 * H;
+  const int slot = (r >= 0 && r < R) ? row_slot[r] : -1;
+  if (slot < 0 || slot >= max_slots) {          // a padding row of a captured step, or a bad row: nothing to do
+    if (r < 0 || r >= R) { if (threadIdx.x == 0) fmx_set_status(status, FMX_BAD_ROW, r, t); }
+    else if (slot >= max_slots && threadIdx.x == 0) fmx_set_status(status, FMX_BAD_SLOT, slot, t);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) oq[c] = 0.f;
+    for (int c = threadIdx.x; c < 2 * H; c += blockDim.x) og[c] = 0.f;
+    return;
+  }
+  const int first = row_start[r];
+  const int i = t - first;                       // the token's place in its portion
+  const float* cstate = state + (long long)slot * slot_stride + conv_off;     // [taps-1, C]
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int n = i - (taps - 1) + j;
+      const float x = n >= 0 ? to_f(proj[(long long)(first + n) * stride + c]) : cstate[(long long)(taps - 1 + n) * C + c];
+      acc = fmaf(conv_w[(long long)c * taps + j], x, acc);
+    }
+    vals[c] = silu_f(acc);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float qscale = 1.0f / sqrtf((float)D);
+  for (int h = warp; h < 2 * G; h += 4) {        // q heads, then k heads
+    const float* v = vals + (long long)h * D;
+    float ss = 0.f;
+    for (int e = lane; e < D; e += 32) ss = fmaf(v[e], v[e], ss);
+    const float inv = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
+    const float mul = h < G ? inv * qscale : inv;
+    for (int e = lane; e < D; e += 32) oq[(long long)h * D + e] = v[e] * mul;
+  }
+  for (int c = 2 * G * D + threadIdx.x; c < C; c += blockDim.x) oq[c] = vals[c];
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float b = ab[(long long)t * ab_stride + h];
+    const float a = ab[(long long)t * ab_stride + H + h] + dt_bias[h];
+    const float sp = a > 20.f ? a : log1pf(expf(a));
+    og[h] = expf(-expf(a_log[h]) * sp);
+    og[H + h] = 1.0f / (1.0f + expf(-b));
+  }
+}
+
+// One thread per (request, channel): the last taps-1 inputs of the request's portion (reaching back into the old
+// state where the portion is shorter) become the new state.
+template <typename T>
+__global__ void conv_state_update_kernel(const T* proj, long long stride, const int* row_start, const int* row_slot,
+                                         float* state, long long slot_stride, long long conv_off, int C, int taps,
+                                         int max_slots) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int slot = row_slot[r];
+  if (c >= C || slot < 0 || slot >= max_slots) return;
+  const int first = row_start[r], n = row_start[r + 1] - first;
+  float* cs = state + (long long)slot * slot_stride + conv_off;
+  float keep[MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) {
+    if (j < taps - 1) {
+      const int p = n - (taps - 1) + j;
+      keep[j] = p >= 0 ? to_f(proj[(long long)(first + p) * stride + c]) : cs[(long long)(taps - 1 + p) * C + c];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j)
+    if (j < taps - 1) cs[(long long)j * C + c] = keep[j];
+}
+
+// grid (ceil(Dv / 16), H, R), 128 threads: 16 columns of S, 8 lanes each; lane `sub` of a column holds rows
+// d = sub * NPL + i, i < NPL (D <= 8 NPL).  qkv [T, C] and gb [T, 2H] as delta_prepare left them; out [T, H*Dv].
+template <int NPL>
+__global__ void __launch_bounds__(128)
+delta_rule_kernel(const float* qkv, const float* gb, const int* row_start, const int* row_slot, float* state,
+                  long long slot_stride, float* out, int H, int G, int D, int Dv, int max_slots) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.z, h = blockIdx.y;
+  const int col = blockIdx.x * 16 + (threadIdx.x >> 3), sub = threadIdx.x & 7;
+  const int slot = row_slot[r];
+  if (slot < 0 || slot >= max_slots) return;
+  const int first = row_start[r], n = row_start[r + 1] - first;
+  const int C = 2 * G * D + H * Dv;
+  const int g = h / (H / G);
+  const bool live = col < Dv;
+  const int colc = live ? col : Dv - 1;          // lanes beyond the last column follow it and write nothing
+  float* sp = state + (long long)slot * slot_stride + ((long long)h * Dv + colc) * D;
+  float S[NPL], k[NPL], q[NPL], kn[NPL], qn[NPL];
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int d = sub * NPL + i;
+    S[i] = d < D ? sp[d] : 0.f;
+  }
+  const long long qoff = (long long)g * D, koff = (long long)(G + g) * D, voff = (long long)2 * G * D + (long long)h * Dv + colc;
+  float vn = 0.f, gn = 0.f, bn = 0.f;
+  auto load = [&](int tok) {
+    const float* p = qkv + (long long)tok * C;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int d = sub * NPL + i;
+      kn[i] = d < D ? p[koff + d] : 0.f;
+      qn[i] = d < D ? p[qoff + d] : 0.f;
+    }
+    vn = p[voff];
+    gn = gb[(long long)tok * 2 * H + h];
+    bn = gb[(long long)tok * 2 * H + H + h];
+  };
+  if (n > 0) load(first);
+  for (int i0 = 0; i0 < n; ++i0) {
+    const int tok = first + i0;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) { k[i] = kn[i]; q[i] = qn[i]; }
+    const float v = vn, gd = gn, beta = bn;
+    if (i0 + 1 < n) load(tok + 1);
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      S[i] *= gd;
+      dot = fmaf(S[i], k[i], dot);
+    }
+    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+    dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+    const float u = beta * (v - dot);
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      S[i] = fmaf(k[i], u, S[i]);
+      o = fmaf(S[i], q[i], o);
+    }
+    o += __shfl_xor_sync(0xffffffffu, o, 1);
+    o += __shfl_xor_sync(0xffffffffu, o, 2);
+    o += __shfl_xor_sync(0xffffffffu, o, 4);
+    if (live && sub == 0) out[(long long)tok * H * Dv + (long long)h * Dv + col] = o;
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int d = sub * NPL + i;
+      if (d < D) sp[d] = S[i];
+    }
+  }
+}
+
+// One warp per (token, head): out[t, h, :] = o / sqrt(mean(o^2) + eps) * w * silu(gate[t, h, :]).
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_rmsnorm_kernel(const float* o, const T* gate, long long gate_stride, const float* __restrict__ w, T* out,
+                     long long out_stride, long long n_items, int H, int Dv, float eps) {
+  pdl_wait();
+  pdl_trigger();
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= n_items) return;
+  const long long t = item / H;
+  const int h = (int)(item - t * H);
+  const float* op = o + (t * H + h) * Dv;
+  const T* gp = gate + t * gate_stride + (long long)h * Dv;
+  T* dst = out + t * out_stride + (long long)h * Dv;
+  float ss = 0.f;
+  for (int e = lane; e < Dv; e += 32) ss = fmaf(op[e], op[e], ss);
+  const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)Dv + eps);
+  for (int e = lane; e < Dv; e += 32) dst[e] = from_f<T>(op[e] * rstd * w[e] * silu_f(to_f(gp[e])));
+}
+}  // namespace
+
+FMX_EXPORT int fmx_delta_prepare(const void* proj, long long stride, const float* ab, long long ab_stride,
+                                 const float* conv_w, const float* a_log, const float* dt_bias, const int* token_row,
+                                 const int* row_start, const int* row_slot, float* state, long long slot_stride,
+                                 long long conv_off, float* out_qkv, float* out_gb, int T, int R, int H, int G, int D, int Dv,
+                                 int taps, int max_slots, int dtype, int* status, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || R <= 0 || H <= 0 || G <= 0 || H % G || D <= 0 || Dv <= 0 || taps < 1 || taps > MAX_TAPS)
+    return fmx_fail("fmx_delta_prepare: bad sizes T=%d R=%d H=%d G=%d D=%d Dv=%d taps=%d", T, R, H, G, D, Dv, taps);
+  const int C = 2 * G * D + H * Dv;
+  if (stride < C || ab_stride < 2 * H) return fmx_fail("fmx_delta_prepare: rows too narrow");
+  const size_t smem = (size_t)C * sizeof(float);
+  if (smem > 200 * 1024) return fmx_fail("fmx_delta_prepare: %d channels do not fit shared memory", C);
+#define FMX_DELTA_PREP(TT)                                                                                             \
+  do {                                                                                                                 \
+    if (smem > 48 * 1024)                                                                                              \
+      cudaFuncSetAttribute(delta_prepare_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+    fmx_launch(delta_prepare_kernel<TT>, dim3(T), dim3(128), smem, stream, (const TT*)proj, stride, ab, ab_stride, conv_w, \
+               a_log, dt_bias, token_row, row_start, row_slot, (const float*)state, slot_stride, conv_off, out_qkv,    \
+               out_gb, H, G, D, Dv, taps, R, max_slots, status);                                                       \
+    fmx_launch(conv_state_update_kernel<TT>, dim3((C + 127) / 128, R), dim3(128), 0, stream, (const TT*)proj, stride,  \
+               row_start, row_slot, state, slot_stride, conv_off, C, taps, max_slots);                                 \
+  } while (0)
+  if (dtype == FMX_F32)
+    FMX_DELTA_PREP(float);
+  else if (dtype == FMX_BF16)
+    FMX_DELTA_PREP(bf16);
+  else
+    return fmx_fail("fmx_delta_prepare: unknown dtype %d", dtype);
+#undef FMX_DELTA_PREP
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
+FMX_EXPORT int fmx_delta_rule(const float* qkv, const float* gb, const int* row_start, const int* row_slot, float* state,
+                              long long slot_stride, float* out, int R, int H, int G, int D, int Dv, int max_slots,
+                              cudaStream_t stream) {
+  if (R == 0) return 0;
+  if (R < 0 || H <= 0 || G <= 0 || H % G || D <= 0 || Dv <= 0 || D > 256)
+    return fmx_fail("fmx_delta_rule: bad sizes R=%d H=%d G=%d D=%d Dv=%d", R, H, G, D, Dv);
+  if (H > 65535 || R > 65535) return fmx_fail("fmx_delta_rule: batch too large");
+  const dim3 grid((Dv + 15) / 16, H, R), block(128);
+#define FMX_DELTA_RULE(NPL)                                                                                            \
+  fmx_launch(delta_rule_kernel<NPL>, grid, block, 0, stream, qkv, gb, row_start, row_slot, state, slot_stride, out, H, \
+             G, D, Dv, max_slots)
+  if (D <= 16) FMX_DELTA_RULE(2);
+  else if (D <= 32) FMX_DELTA_RULE(4);
+  else if (D <= 64) FMX_DELTA_RULE(8);
+  else if (D <= 128) FMX_DELTA_RULE(16);
+  else FMX_DELTA_RULE(32);
+#undef FMX_DELTA_RULE
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
+FMX_EXPORT int fmx_gated_rmsnorm(const float* o, const void* gate, long long gate_stride, const float* w, void* out,
+                                 long long out_stride, int T, int H, int Dv, float eps, int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || H <= 0 || Dv <= 0) return fmx_fail("fmx_gated_rmsnorm: bad sizes T=%d H=%d Dv=%d", T, H, Dv);
+  const long long items = (long long)T * H;
+  const long long grid = (items + 3) / 4;
+  if (grid > 2147483647LL) return fmx_fail("fmx_gated_rmsnorm: batch too large");
+  if (dtype == FMX_F32)
+    fmx_launch(gated_rmsnorm_kernel<float>, dim3((unsigned)grid), dim3(128), 0, stream, o, (const float*)gate, gate_stride, w,
+               (float*)out, out_stride, items, H, Dv, eps);
+  else if (dtype == FMX_BF16)
+    fmx_launch(gated_rmsnorm_kernel<bf16>, dim3((unsigned)grid), dim3(128), 0, stream, o, (const bf16*)gate, gate_stride, w,
+               (bf16*)out, out_stride, items, H, Dv, eps);
+  else
+    return fmx_fail("fmx_gated_rmsnorm: unknown dtype %d", dtype);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}

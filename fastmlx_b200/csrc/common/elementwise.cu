@@ -1,5 +1,6 @@
 // Row gather (token embedding, and the choice of the rows whose logits are wanted),
 // RMSNorm with the residual sum in front of it, and SiLU-and-multiply.
+#include <math.h>
 #include "common.cuh"
 
 // out[t, :] = table[ids[t], :].  A bad id leaves a status code and a row of zeros.
@@ -327,6 +328,47 @@ FMX_EXPORT int fmx_fill_rows(const float* vec, void* out, int rows, int cols, lo
     fmx_launch(fill_rows_kernel<bf16>, dim3(grid), dim3(block), 0, stream, vec, (bf16*)out, (long long)rows, cols, ldo);
   else
     return fmx_fail("fmx_fill_rows: unknown dtype %d", dtype);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
+// Elementwise activations of a feed-forward's hidden layer, over rows that may be slices of wider buffers.
+// kind 0: relu(x)^2; 1: gelu, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))); 2: silu.
+namespace {
+template <typename T>
+__global__ void activation_kernel(const T* x, long long x_stride, T* out, long long out_stride, long long rows, int cols,
+                                  int kind) {
+  pdl_wait();
+  pdl_trigger();
+  const long long n = rows * cols;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / cols;
+    const int c = (int)(idx - r * cols);
+    const float v = to_f(x[r * x_stride + c]);
+    float y;
+    if (kind == 0) { const float p = fmaxf(v, 0.f); y = p * p; }
+    else if (kind == 1) y = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    else y = v / (1.0f + expf(-v));
+    out[r * out_stride + c] = from_f<T>(y);
+  }
+}
+}  // namespace
+
+FMX_EXPORT int fmx_activation(const void* x, long long x_stride, void* out, long long out_stride, int rows, int cols,
+                              int kind, int dtype, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return 0;
+  if (rows < 0 || cols < 0 || kind < 0 || kind > 2) return fmx_fail("fmx_activation: bad arguments rows=%d cols=%d kind=%d", rows, cols, kind);
+  const long long n = (long long)rows * cols, cap = (long long)fmx_num_sms() * 16;
+  const int block = 256;
+  const int grid = (int)((n + block - 1) / block < cap ? (n + block - 1) / block : cap);
+  if (dtype == FMX_F32)
+    fmx_launch(activation_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)x, x_stride, (float*)out, out_stride,
+               (long long)rows, cols, kind);
+  else if (dtype == FMX_BF16)
+    fmx_launch(activation_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)x, x_stride, (bf16*)out, out_stride,
+               (long long)rows, cols, kind);
+  else
+    return fmx_fail("fmx_activation: unknown dtype %d", dtype);
   FMX_LAUNCH_CHECK();
   return 0;
 }

@@ -1,0 +1,121 @@
+// Queries and keys made ready for attention in one pass: rotary positions on the first `rot`
+// dimensions of every head, then (optionally) each head divided by its root mean square, then
+// the keys and values written into the layer's pages.
+//
+// qkv is [T, nh*hd + nkv*hd + nkv*vd] as the projection left it (biases added).  The queries
+// leave in 32-bit, [T, nh*hd]: scores are then taken from unrounded queries.  Keys and values go
+// to slot_mapping[t] of a cache whose pages hold [nkv, page_size, hd] keys followed by
+// [nkv, page_size, vd] values.  Angles (position * inv_freq[j]), sines, cosines, the sum of
+// squares and the division are 32-bit; the sum of squares of a head is taken in an order that
+// depends on the head size alone.
+#include "common.cuh"
+
+namespace {
+constexpr int QKP_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(QKP_WARPS * 32)
+qk_prepare_kernel(const T* qkv, long long row_stride, const int* positions, const float* __restrict__ inv_freq,
+                  const long long* slot_mapping, float* q_out, T* kv, int nh, int nkv, int hd, int vd, int rot,
+                  int interleaved, float norm_eps, int page_size, long long num_pages, int* status) {
+  extern __shared__ float smem[];               // [rot/2] sines, [rot/2] cosines, then a head per warp
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int half = rot / 2;
+  float* sn = smem;
+  float* cs = smem + half;
+  float* buf = smem + rot + warp * hd;
+  const T* row = qkv + (long long)t * row_stride;
+  const float pos = (float)positions[t];
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &sn[j], &cs[j]);
+  long long slot = (kv != nullptr && slot_mapping != nullptr) ? slot_mapping[t] : -1;
+  if (slot >= num_pages * page_size) {
+    if (threadIdx.x == 0) fmx_set_status(status, FMX_BAD_SLOT, slot, t);
+    slot = -1;
+  }
+  const long long page = slot >= 0 ? slot / page_size : 0;
+  const int off = slot >= 0 ? (int)(slot - page * page_size) : 0;
+  const long long page_elems = (long long)nkv * page_size * (hd + vd);
+  __syncthreads();
+  for (int h = warp; h < nh + nkv; h += QKP_WARPS) {
+    const T* src = row + (long long)h * hd;
+    for (int e = lane; e < hd; e += 32) buf[e] = to_f(src[e]);
+    __syncwarp();
+    float ss = 0.f;
+    float val[8];                               // head sizes up to 256
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int e = lane + 32 * i;
+      float v = 0.f;
+      if (e < hd) {
+        v = buf[e];
+        if (e < rot) {
+          int j, other;
+          bool first;
+          if (interleaved) { j = e >> 1; first = (e & 1) == 0; other = first ? e + 1 : e - 1; }
+          else { first = e < half; j = first ? e : e - half; other = first ? e + half : e - half; }
+          float x, y;
+          if (first) rope_pair(v, buf[other], sn[j], cs[j], x, y);
+          else rope_pair(buf[other], v, sn[j], cs[j], y, x);      // x: this element's new value in either case
+          v = x;
+        }
+        ss = fmaf(v, v, ss);
+      }
+      val[i] = v;
+    }
+    float mul = 1.0f;
+    if (norm_eps >= 0.f) mul = 1.0f / sqrtf(warp_sum(ss) / (float)hd + norm_eps);
+    if (h < nh) {
+      float* dst = q_out + ((long long)t * nh + h) * hd;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        if (e < hd) dst[e] = val[i] * mul;
+      }
+    } else if (slot >= 0) {
+      T* dst = kv + page * page_elems + ((long long)(h - nh) * page_size + off) * hd;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        if (e < hd) dst[e] = from_f<T>(val[i] * mul);
+      }
+    }
+    __syncwarp();
+  }
+  if (slot < 0) return;
+  const T* vsrc = row + (long long)(nh + nkv) * hd;
+  T* vdst = kv + page * page_elems + (long long)nkv * page_size * hd;
+  for (int it = threadIdx.x; it < nkv * vd; it += blockDim.x) {
+    const int g = it / vd, e = it - g * vd;
+    vdst[((long long)g * page_size + off) * vd + e] = vsrc[it];
+  }
+}
+}  // namespace
+
+// rot = 0: nothing is rotated; norm_eps < 0: heads are not normalised; kv or slot_mapping null:
+// nothing is stored (a layer that reads another's cache then passes nkv = 0 as well).
+FMX_EXPORT int fmx_qk_prepare(const void* qkv, long long row_stride, const int* positions, const float* inv_freq,
+                              const long long* slot_mapping, float* q_out, void* kv, int T, int nh, int nkv, int hd, int vd,
+                              int rot, int interleaved, float norm_eps, int page_size, long long num_pages, int dtype,
+                              int* status, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || nh < 0 || nkv < 0 || hd <= 0 || vd <= 0 || hd > 256 || rot < 0 || rot > hd || (rot & 1) || page_size <= 0)
+    return fmx_fail("fmx_qk_prepare: bad sizes T=%d nh=%d nkv=%d hd=%d vd=%d rot=%d", T, nh, nkv, hd, vd, rot);
+  if (rot > 0 && inv_freq == nullptr) return fmx_fail("fmx_qk_prepare: rot=%d needs a frequency table", rot);
+  if (row_stride < (long long)(nh + nkv) * hd + (long long)nkv * vd) return fmx_fail("fmx_qk_prepare: row stride too small");
+  const size_t smem = ((size_t)rot + (size_t)QKP_WARPS * hd) * sizeof(float);
+  if (dtype == FMX_F32)
+    fmx_launch(qk_prepare_kernel<float>, dim3(T), dim3(QKP_WARPS * 32), smem, stream, (const float*)qkv, row_stride,
+               positions, inv_freq, slot_mapping, q_out, (float*)kv, nh, nkv, hd, vd, rot, interleaved, norm_eps, page_size,
+               num_pages, status);
+  else if (dtype == FMX_BF16)
+    fmx_launch(qk_prepare_kernel<bf16>, dim3(T), dim3(QKP_WARPS * 32), smem, stream, (const bf16*)qkv, row_stride, positions,
+               inv_freq, slot_mapping, q_out, (bf16*)kv, nh, nkv, hd, vd, rot, interleaved, norm_eps, page_size, num_pages,
+               status);
+  else
+    return fmx_fail("fmx_qk_prepare: unknown dtype %d", dtype);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}

@@ -312,6 +312,105 @@ def paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> t
     return out
 
 
+def qk_prepare(qkv, positions, inv_freq, rotary_dim, traditional, norm_eps, slot_mapping, kv, nh, nkv, hd, vd,
+               status) -> torch.Tensor:
+    """Queries and keys of qkv[T, nh*hd + nkv*hd + nkv*vd] made ready for attention: rotated over their
+    first `rotary_dim` dimensions, then (norm_eps not None) each head divided by its root mean square;
+    keys and values are stored at slot_mapping in pages that hold [nkv, page, hd] keys and then
+    [nkv, page, vd] values.  -> the queries in 32-bit, [T, nh*hd]."""
+    _need_cuda(qkv, positions, inv_freq, slot_mapping, kv)
+    assert qkv.dim() == 2 and qkv.stride(1) == 1 and positions.dtype == torch.int32
+    T = qkv.shape[0]
+    q = torch.empty((T, nh * hd), dtype=torch.float32, device=qkv.device)
+    if kv is not None:
+        assert kv.is_contiguous() and kv.dtype == qkv.dtype and slot_mapping is not None and slot_mapping.dtype == torch.int64
+        num_pages = kv.shape[0]
+        page_size = kv[0].numel() // (nkv * (hd + vd))
+    else:
+        num_pages, page_size = 0, 1
+    call("common", "fmx_qk_prepare", qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), _ptr(inv_freq), _ptr(slot_mapping),
+         q.data_ptr(), _ptr(kv), T, nh, nkv if kv is not None else 0, hd, vd, int(rotary_dim), int(bool(traditional)),
+         -1.0 if norm_eps is None else float(norm_eps), page_size, num_pages, _dt(qkv), _ptr(status), _stream())
+    return q
+
+
+def paged_attention_general(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, window, page_size, out=None) -> torch.Tensor:
+    """Attention with 32-bit scores and weights, one warp per (token, head): queries q[T, nh*hd] of their own
+    type over pages of [nkv, page, hd] keys and [nkv, page, vd] values; scores are capped by
+    softcap * tanh(s / softcap) where softcap > 0.  `out` may be a slice of a wider buffer.  -> [T, nh*vd]."""
+    _need_cuda(q, kv)
+    assert kv.is_contiguous() and q.stride(1) == 1
+    T = q.shape[0]
+    if out is None:
+        out = torch.empty((T, nh * vd), dtype=kv.dtype, device=q.device)
+    assert out.dtype == kv.dtype and out.stride(1) == 1 and out.shape == (T, nh * vd)
+    bt = group.block_tables
+    call("common", "fmx_paged_attention_general", q.data_ptr(), q.stride(0), _dt(q), kv.data_ptr(), bt.data_ptr(),
+         bt.stride(0), ctx.token_row.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), out.stride(0), T, nh, nkv, hd, vd,
+         int(page_size), kv.shape[0], float(scale), float(softcap or 0.0), int(window), bt.shape[0], _dt(kv),
+         _ptr(ctx.status), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- gated delta rule
+def delta_prepare(proj, ab, conv_w, a_log, dt_bias, ctx, state, conv_off, H, G, D, Dv, taps):
+    """What the recurrence of a gated delta rule layer takes in, from the projections of a step:
+    proj[T, >= C] holds q (G*D) | k (G*D) | v (H*Dv) channels, ab[T, 2H] in 32-bit the write strengths'
+    and decays' pre-activations.  Channels pass a causal convolution of `taps` taps (weights conv_w[C, taps];
+    inputs before a portion's start come from the request's state slot, which then takes the
+    portion's last inputs) and SiLU; q and k become unit vectors per head, q times D^-1/2.
+    -> (q | k | v in 32-bit [T, C], decay | beta in 32-bit [T, 2H])."""
+    _need_cuda(proj, ab, conv_w, a_log, dt_bias, state)
+    T = proj.shape[0]
+    C = 2 * G * D + H * Dv
+    assert proj.stride(1) == 1 and ab.dtype == torch.float32 and ab.stride(1) == 1 and state.dtype == torch.float32
+    assert conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape == (C, taps) and state.is_contiguous()
+    qkv = torch.empty((T, C), dtype=torch.float32, device=proj.device)
+    gb = torch.empty((T, 2 * H), dtype=torch.float32, device=proj.device)
+    call("common", "fmx_delta_prepare", proj.data_ptr(), proj.stride(0), ab.data_ptr(), ab.stride(0), conv_w.data_ptr(),
+         a_log.data_ptr(), dt_bias.data_ptr(), ctx.token_row.data_ptr(), ctx.row_start.data_ptr(), ctx.row_slot.data_ptr(),
+         state.data_ptr(), state.stride(0), int(conv_off), qkv.data_ptr(), gb.data_ptr(), T, ctx.R, H, G, D, Dv, int(taps),
+         state.shape[0], _dt(proj), _ptr(ctx.status), _stream())
+    return qkv, gb
+
+
+def delta_rule(qkv, gb, ctx, state, H, G, D, Dv) -> torch.Tensor:
+    """The gated delta rule over every request's tokens of the step, in order, from and into the requests'
+    state slots (S^T per head, [H, Dv, D], at the head of a slot): S <- g S; u = beta (v - S^T k);
+    S <- S + k u^T; o = S^T q.  -> o in 32-bit, [T, H*Dv]."""
+    T = qkv.shape[0]
+    out = torch.empty((T, H * Dv), dtype=torch.float32, device=qkv.device)
+    call("common", "fmx_delta_rule", qkv.data_ptr(), gb.data_ptr(), ctx.row_start.data_ptr(), ctx.row_slot.data_ptr(),
+         state.data_ptr(), state.stride(0), out.data_ptr(), ctx.R, H, G, D, Dv, state.shape[0], _stream())
+    return out
+
+
+def gated_rmsnorm(o, gate, weight, eps, H, Dv, out_dtype, out=None) -> torch.Tensor:
+    """o[T, H*Dv] (32-bit) per head divided by its root mean square, times weight[Dv], times silu(gate);
+    gate and out may be slices of wider buffers."""
+    T = o.shape[0]
+    if out is None:
+        out = torch.empty((T, H * Dv), dtype=out_dtype, device=o.device)
+    assert gate.stride(1) == 1 and out.stride(1) == 1 and gate.dtype == out.dtype and o.is_contiguous()
+    call("common", "fmx_gated_rmsnorm", o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(), out.data_ptr(),
+         out.stride(0), T, H, Dv, float(eps), _dt(out), _stream())
+    return out
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x, kind: str, out=None) -> torch.Tensor:
+    """relu(x)^2, gelu (tanh form) or silu, in 32-bit, over rows that may be slices of wider buffers."""
+    _need_cuda(x)
+    if out is None:
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    assert x.dim() == 2 and x.stride(1) == 1 and out.stride(1) == 1 and out.shape == x.shape and out.dtype == x.dtype
+    call("common", "fmx_activation", x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), x.shape[0], x.shape[1],
+         ACTIVATIONS[kind], _dt(x), _stream())
+    return out
+
+
 MAX_SPLITS = 64
 ATTN_SCRATCH_FLOATS = 8 << 20        # 32 MiB of split partials per device
 _scratch: dict = {}

@@ -32,6 +32,14 @@ _SIGNATURES = {
         "fmx_filter_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
         "fmx_penalties": [_P, _L, _I, _I, _P, _I, _P, _P, _P, _P, _P],
         "fmx_logit_bias": [_P, _L, _I, _P, _P, _P, _I, _P],
+        "fmx_paged_attention_general": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _L, _F, _F, _I, _I,
+                                        _I, _P, _P],
+        "fmx_qk_prepare": [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _L, _I, _P, _P],
+        "fmx_delta_prepare": [_P, _L, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
+                              _P, _P],
+        "fmx_delta_rule": [_P, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _I, _P],
+        "fmx_gated_rmsnorm": [_P, _P, _L, _P, _P, _L, _I, _I, _I, _F, _I, _P],
+        "fmx_activation": [_P, _L, _P, _L, _I, _I, _I, _I, _P],
     },
     "bf16": {
         "fmx_gemv": [_P, _L, _P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P],

@@ -1,2 +1,3 @@
 """Architectures.  Importing this package registers them."""
 from . import llama  # noqa: F401
+from . import medirax  # noqa: F401

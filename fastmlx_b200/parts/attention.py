@@ -16,6 +16,13 @@ class GQAAttention(Mixer):
     pages alone, so a token's result does not depend on how the tokens were cut into steps.
     With `share_kv=True` the part has no k/v projections and reads the cache of the
     schedule entry it is pointed at.
+
+    Three further choices put a layer on the route with 32-bit scores and weights (`qk_prepare`
+    and `paged_attention_general`): `softcap` c > 0 caps the scaled scores, s <- c tanh(s / c);
+    `qk_norm_eps` divides q and k, after their rotation, by their root mean square over the head
+    (no weight); `v_head_dim` gives values another width than keys.  There the queries stay in
+    32-bit from the rotation to the scores.  `output=False` leaves the output projection to the
+    block (`out_piece` names its tensors), which may join it with the feed-forward's.
     """
 
     supports_cuda_graph = True
@@ -23,10 +30,16 @@ class GQAAttention(Mixer):
     def __init__(self, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  pos: PositionEncoding, name: str, bias: bool = False, scale: float | None = None,
                  window: int = 0, share_kv: bool = False,
-                 proj_names=("q_proj", "k_proj", "v_proj", "o_proj")):
+                 proj_names=("q_proj", "k_proj", "v_proj", "o_proj"), v_head_dim: int | None = None,
+                 softcap: float = 0.0, qk_norm_eps: float | None = None, output: bool = True,
+                 weight_suffix: str = ".weight", bias_suffix: str = ".bias"):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are no multiple of {num_kv_heads} kv heads")
         self.nh, self.nkv, self.hd = int(num_heads), int(num_kv_heads), int(head_dim)
+        self.vd = int(v_head_dim) if v_head_dim else self.hd
+        self.softcap = float(softcap or 0.0)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.general = self.softcap > 0 or self.qk_norm_eps is not None or self.vd != self.hd
         self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
         self.window = int(window)
         self.share_kv = bool(share_kv)
@@ -34,18 +47,40 @@ class GQAAttention(Mixer):
         qn, kn, vn, on = (f"{name}.{p}" for p in proj_names)
         outs = [(qn, self.nh * self.hd)]
         if not share_kv:
-            outs += [(kn, self.nkv * self.hd), (vn, self.nkv * self.hd)]
-        self.qkv = Linear(width, outs, bias)
-        self.o = Linear(self.nh * self.hd, [(on, width)], bias)
+            outs += [(kn, self.nkv * self.hd), (vn, self.nkv * self.vd)]
+        self.qkv = Linear(width, outs, bias, weight_suffix=weight_suffix, bias_suffix=bias_suffix)
+        self.inner_features = self.nh * self.vd
+        self.out_piece = (on + weight_suffix, self.inner_features, on + bias_suffix if bias else None)
+        self.o = Linear(self.inner_features, [(on, width)], bias, weight_suffix=weight_suffix,
+                        bias_suffix=bias_suffix) if output else None
 
     def children(self):
-        return (self.qkv, self.o, self.pos)
+        return tuple(p for p in (self.qkv, self.o, self.pos) if p is not None)
 
     def cache_spec(self):
-        return PagedKVSpec(self.nkv, self.hd, self.window)
+        return PagedKVSpec(self.nkv, self.hd, self.window, 0 if self.vd == self.hd else self.vd)
 
     def forward(self, x, ctx, cache):
-        return self.o.forward(self._attend(self.qkv.forward(x), ctx, cache))
+        return self.o.forward(self.forward_inner(x, ctx, cache))
+
+    def forward_inner(self, x, ctx, cache, out=None):
+        """The heads' outputs side by side, [T, nh * v width], before the output projection; into
+        `out` (a slice of a wider buffer) where one is given."""
+        qkv = self.qkv.forward(x)
+        if not self.general:
+            res = self._attend(qkv, ctx, cache)
+            if out is None:
+                return res
+            out.copy_(res)
+            return out
+        k = self.rt.k
+        inv_freq, rot, trad = self.pos.native_args()
+        g = ctx.groups[cache.group]
+        store = cache.writable and not self.share_kv
+        q = k.qk_prepare(qkv, ctx.positions, inv_freq, rot, trad, self.qk_norm_eps, g.slot_mapping if store else None,
+                         cache.kv if store else None, self.nh, self.nkv, self.hd, self.vd, ctx.status)
+        return k.paged_attention_general(q, cache.kv, ctx, g, self.nh, self.nkv, self.hd, self.vd, self.scale,
+                                         self.softcap, self.window, g.page_size, out=out)
 
     def _attend(self, qkv, ctx, cache):
         k = self.rt.k
@@ -66,6 +101,9 @@ class GQAAttention(Mixer):
     def emit(self, b, x, pos):
         from ..engine.native import BF16, NotNative, OP_ATTENTION, _fn
         from ..kernels import lib as klib
+        if self.general or self.o is None:
+            raise NotNative("capped scores, normalised q and k, values of another width and a joined output "
+                            "projection run in Python only")
         cache = b.manager.entries[pos]
         if cache.kv is None:
             raise NotNative("an attention layer without pages")

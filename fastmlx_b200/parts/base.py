@@ -31,10 +31,17 @@ class WeightSpec:
 @dataclass(frozen=True)
 class PagedKVSpec:
     """A mixer that keeps keys and values of earlier tokens in pages.  `window` = 0
-    keeps every key; w > 0 only the last w (the page manager gives older pages back)."""
+    keeps every key; w > 0 only the last w (the page manager gives older pages back).
+    `v_head_dim` = 0: values are as wide as keys; else a page holds its keys
+    [kv heads, page, head_dim] followed by its values [kv heads, page, v_head_dim]."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -58,7 +65,9 @@ class Runtime:
 
 
 class Part:
-    """Base of all parts: a tree whose leaves declare tensors.
+    """Base of all parts: a tree whose leaves declare tensors.  `kind` of a WeightSpec also takes
+    "norm0" (a norm weight stored around zero), "conv" (taps of a short convolution), "log_rate"
+    and "rate_bias" (the logarithm of a decay rate and the bias of its step size).
 
     A part may also describe what it does to the native step executor (`emit`, writing
     operations over numbered activation buffers to an `engine.native.ProgramBuilder`); a part

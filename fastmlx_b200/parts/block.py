@@ -1,7 +1,10 @@
 """The arrangement of norm, mixer and feed-forward in one layer."""
 from __future__ import annotations
 
+import torch
+
 from .base import FeedForward, Mixer, Norm, Part
+from .linear import JoinedLinear
 
 
 class PreNormBlock(Part):
@@ -39,3 +42,40 @@ class PreNormBlock(Part):
         z = self.ffn.emit(b, x)
         b.release(x)
         return z, stream
+
+
+class ParallelBlock(Part):
+    """h = norm(x); x <- x + (mixer(h) + ffn(h)): one norm, and both sublayers read its output.
+
+    Mixer and feed-forward are built with `output=False`: their output projections are joined
+    into one product over [mixer's heads | feed-forward's hidden layer], so that the two
+    sublayers' outputs are added inside the product's 32-bit accumulators, and the block's
+    output is rounded once before the 32-bit residual sum takes it.  `ffn` may be None."""
+
+    def __init__(self, mixer: Mixer, ffn: FeedForward | None, norm: Norm, width: int):
+        self.mixer, self.ffn, self.norm = mixer, ffn, norm
+        pieces = [mixer.out_piece] + ([ffn.out_piece] if ffn is not None else [])
+        self.out = JoinedLinear(width, pieces)
+
+    def children(self):
+        return tuple(p for p in (self.norm, self.mixer, self.ffn, self.out) if p is not None)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def state_spec(self):
+        return self.mixer.state_spec()
+
+    @property
+    def supports_cuda_graph(self):
+        return bool(getattr(self.mixer, "supports_cuda_graph", False)) and \
+            bool(getattr(self.ffn, "supports_cuda_graph", True))
+
+    def forward(self, delta, residual, ctx, cache):
+        h, residual = self.norm.forward(delta, residual)
+        joined = torch.empty((h.shape[0], self.out.in_features), dtype=self.rt.dtype, device=h.device)
+        m = self.mixer.inner_features
+        self.mixer.forward_inner(h, ctx, cache, out=joined[:, :m] if self.ffn is not None else joined)
+        if self.ffn is not None:
+            self.ffn.forward_inner(h, ctx, out=joined[:, m:])
+        return self.out.forward(joined), residual

@@ -9,15 +9,16 @@ from .base import Part, Runtime, WeightSpec, to_compute
 class Embedding(Part):
     """h[t] = E[id_t], no scaling (tamnd/fastmlx compute/models/llama.go:385-390)."""
 
-    def __init__(self, vocab: int, width: int, name: str):
+    def __init__(self, vocab: int, width: int, name: str, suffix: str = ".weight"):
         self.vocab, self.width, self.name = int(vocab), int(width), name
+        self.tensor = name + suffix
         self.weight = None
 
     def own_weight_specs(self):
-        return [WeightSpec(self.name + ".weight", (self.vocab, self.width), "embedding")]
+        return [WeightSpec(self.tensor, (self.vocab, self.width), "embedding")]
 
     def bind_own(self, tensors, rt: Runtime):
-        self.weight = to_compute(tensors[self.name + ".weight"], rt)
+        self.weight = to_compute(tensors[self.tensor], rt)
 
     def weight_bytes(self):
         return 0          # a step reads T rows, not the table
@@ -40,18 +41,22 @@ class LMHead(Part):
     model ties them (tamnd/fastmlx compute/models/llama.go:433-437).  Only the rows whose
     logits are wanted reach it."""
 
-    def __init__(self, vocab: int, width: int, name: str | None, tied: Embedding | None = None):
+    def __init__(self, vocab: int, width: int, name: str | None, tied: Embedding | None = None,
+                 suffix: str = ".weight", scale: float = 1.0):
+        """`scale`: a constant the logits are multiplied by (in 32-bit, after the product)."""
         if (name is None) == (tied is None):
             raise ValueError("LMHead takes either a tensor name or an embedding to tie to")
         self.vocab, self.width, self.name, self.tied = int(vocab), int(width), name, tied
+        self.tensor = None if name is None else name + suffix
+        self.scale = float(scale)
         self.weight = None
 
     def own_weight_specs(self):
-        return [] if self.tied is not None else [WeightSpec(self.name + ".weight", (self.vocab, self.width), "matrix")]
+        return [] if self.tied is not None else [WeightSpec(self.tensor, (self.vocab, self.width), "matrix")]
 
     def bind_own(self, tensors, rt: Runtime):
         if self.tied is None:
-            self.weight = to_compute(tensors[self.name + ".weight"], rt)
+            self.weight = to_compute(tensors[self.tensor], rt)
 
     def weight_bytes(self):
         w = self.tied.weight if self.tied is not None else self.weight
@@ -59,7 +64,10 @@ class LMHead(Part):
 
     def forward(self, x):
         w = self.tied.weight if self.tied is not None else self.weight
-        return self.rt.k.linear(x, w, None, torch.float32)
+        logits = self.rt.k.linear(x, w, None, torch.float32)
+        if self.scale != 1.0:
+            logits.mul_(self.scale)
+        return logits
 
     def forward_after(self, delta, residual, norm, greedy: bool = False):
         """Final norm, then logits; `greedy`: the index of each row's largest logit instead
@@ -69,13 +77,15 @@ class LMHead(Part):
             return self.forward(x)
         k = self.rt.k
         w = self.tied.weight if self.tied is not None else self.weight
-        if hasattr(k, "can_greedy_head") and k.can_greedy_head(x, w):
-            return k.greedy_head(x, w)
+        if self.scale > 0 and hasattr(k, "can_greedy_head") and k.can_greedy_head(x, w):
+            return k.greedy_head(x, w)                # a positive scale does not change the choice
         return k.argmax(self.forward(x))
 
     def emit_after(self, b, delta, stream, norm) -> None:
         """Native program: final norm, then the step's logits."""
-        from ..engine.native import F32, LOGITS, OP_LINEAR, _dt
+        from ..engine.native import F32, LOGITS, NotNative, OP_LINEAR, _dt
+        if self.scale != 1.0:
+            raise NotNative("the native executor's head does not scale its logits")
         x, _ = norm.emit(b, delta, stream)
         w = self.tied.weight if self.tied is not None else self.weight
         b.op(OP_LINEAR, in0=x, out0=LOGITS, w=b.ptr(w), w_dtype=_dt(w.dtype), ldw=w.stride(0), n=self.vocab, k=self.width,

@@ -12,8 +12,10 @@ class Linear(Part):
     gate/up run as one matrix product (tamnd/fastmlx runs them one by one,
     compute/models/llama.go:403-405,426-427, through compute/models/qwen3_forward.go:111-115)."""
 
-    def __init__(self, in_features: int, names, bias: bool = False, interleave: int = 0):
-        """`interleave` = b > 0 (two matrices of equal height, a multiple of b): their rows are
+    def __init__(self, in_features: int, names, bias: bool = False, interleave: int = 0,
+                 weight_suffix: str = ".weight", bias_suffix: str = ".bias"):
+        """The suffixes complete a tensor's name (a checkpoint that calls its matrices `x.q` and their
+        biases `x.q.b` passes "" and ".b").  `interleave` = b > 0 (two matrices of equal height, a multiple of b): their rows are
         stacked in alternating blocks of b, so that a tile of 2b output columns holds b rows
         of the first and the matching b rows of the second."""
         self.in_features = int(in_features)
@@ -21,6 +23,7 @@ class Linear(Part):
         self.out_features = sum(o for _, o in self.names)
         self.has_bias = bool(bias)
         self.interleave = int(interleave)
+        self.wsfx, self.bsfx = weight_suffix, bias_suffix
         if self.interleave and (len(self.names) != 2 or self.names[0][1] != self.names[1][1]
                                 or self.names[0][1] % self.interleave):
             raise ValueError("interleaving takes two matrices of equal height, a multiple of the block")
@@ -28,16 +31,16 @@ class Linear(Part):
         self.bias = None
 
     def own_weight_specs(self):
-        specs = [WeightSpec(n + ".weight", (o, self.in_features), "matrix") for n, o in self.names]
+        specs = [WeightSpec(n + self.wsfx, (o, self.in_features), "matrix") for n, o in self.names]
         if self.has_bias:
-            specs += [WeightSpec(n + ".bias", (o,), "bias") for n, o in self.names]
+            specs += [WeightSpec(n + self.bsfx, (o,), "bias") for n, o in self.names]
         return specs
 
     def bind_own(self, tensors, rt: Runtime):
-        ws = [to_compute(tensors[n + ".weight"], rt) for n, _ in self.names]
+        ws = [to_compute(tensors[n + self.wsfx], rt) for n, _ in self.names]
         if len({w.dtype for w in ws}) > 1:
             ws = [w.float() for w in ws]
-        bs = [to_f32_vector(tensors[n + ".bias"], rt) for n, _ in self.names] if self.has_bias else None
+        bs = [to_f32_vector(tensors[n + self.bsfx], rt) for n, _ in self.names] if self.has_bias else None
         if self.interleave:
             b = self.interleave
             ws = [torch.stack([w.view(-1, b, self.in_features) for w in ws], dim=1).reshape(-1, self.in_features)]
@@ -62,3 +65,46 @@ class Linear(Part):
         b.op(OP_LINEAR, in0=x, out0=out, w=b.ptr(self.weight), bias=b.ptr(self.bias), w_dtype=_dt(self.weight.dtype),
              ldw=self.weight.stride(0), n=self.out_features, k=self.in_features, out_dtype=dt)
         return out
+
+
+class JoinedLinear(Part):
+    """Several matrices with the same output applied to inputs laid side by side: y = [x1 | x2 | ...]
+    [W1 | W2 | ...]^T (+ b1 + b2 ...).  The sum of the products x_i W_i^T is then taken inside one
+    product's 32-bit accumulators and rounded once: how a block whose sublayers run side by side adds
+    its mixer's and its feed-forward's outputs.  `pieces`: (weight tensor name, in features, bias
+    tensor name or None); `offsets[i]` is where piece i's inputs start in a row of x."""
+
+    def __init__(self, out_features: int, pieces):
+        self.out_features = int(out_features)
+        self.pieces = [(w, int(k), b) for w, k, b in pieces]
+        self.offsets, at = [], 0
+        for _, k, _ in self.pieces:
+            self.offsets.append(at)
+            at += k
+        self.in_features = at
+        self.weight = None
+        self.bias = None
+
+    def own_weight_specs(self):
+        specs = [WeightSpec(w, (self.out_features, k), "matrix") for w, k, _ in self.pieces]
+        specs += [WeightSpec(b, (self.out_features,), "bias") for _, _, b in self.pieces if b is not None]
+        return specs
+
+    def bind_own(self, tensors, rt: Runtime):
+        ws = [to_compute(tensors[w], rt) for w, _, _ in self.pieces]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.float() for w in ws]
+        self.weight = ws[0].contiguous() if len(ws) == 1 else torch.cat(ws, dim=1).contiguous()
+        bs = [to_f32_vector(tensors[b], rt) for _, _, b in self.pieces if b is not None]
+        self.bias = None
+        if bs:
+            total = bs[0]
+            for b in bs[1:]:
+                total = total + b
+            self.bias = total.contiguous()
+
+    def weight_bytes(self):
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, x, out_dtype=None):
+        return self.rt.k.linear(x, self.weight, self.bias, out_dtype or self.rt.dtype)

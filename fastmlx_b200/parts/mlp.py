@@ -1,4 +1,4 @@
-"""Dense gated feed-forward."""
+"""Dense feed-forwards: gated (SwiGLU) and plain (one hidden layer and an activation)."""
 from __future__ import annotations
 
 import torch
@@ -52,3 +52,32 @@ class SwiGLU(FeedForward):
         out = self.down.emit(b, act)
         b.release(act)
         return out
+
+
+class DenseMLP(FeedForward):
+    """down(act(up(x))) with act one of relu2 (the square of relu), gelu_tanh, silu, computed in
+    32-bit.  `output=False` leaves the down projection to the block (`out_piece` names its tensor),
+    which may join it with the mixer's output projection."""
+
+    def __init__(self, width: int, intermediate: int, name: str, activation: str = "relu2", bias: bool = False,
+                 proj_names=("up", "down"), output: bool = True, weight_suffix: str = ".weight",
+                 bias_suffix: str = ".bias"):
+        if activation not in ("relu2", "gelu_tanh", "silu"):
+            raise ValueError(f"unknown activation {activation!r}")
+        self.width, self.intermediate, self.activation = int(width), int(intermediate), activation
+        u, d = (f"{name}.{p}" for p in proj_names)
+        self.up = Linear(width, [(u, intermediate)], bias, weight_suffix=weight_suffix, bias_suffix=bias_suffix)
+        self.inner_features = self.intermediate
+        self.out_piece = (d + weight_suffix, self.intermediate, d + bias_suffix if bias else None)
+        self.down = Linear(intermediate, [(d, width)], bias, weight_suffix=weight_suffix,
+                           bias_suffix=bias_suffix) if output else None
+
+    def children(self):
+        return tuple(p for p in (self.up, self.down) if p is not None)
+
+    def forward_inner(self, x, ctx, out=None):
+        """The hidden layer after its activation, [T, intermediate]; into `out` where one is given."""
+        return self.rt.k.activation(self.up.forward(x), self.activation, out=out)
+
+    def forward(self, x, ctx):
+        return self.down.forward(self.forward_inner(x, ctx))

@@ -11,14 +11,19 @@ class RMSNorm(Norm):
     (tamnd/fastmlx compute/models/llama.go:402,425,432 -> mlxgo/binding_cgo.go:382-396).
     Sum of squares, rsqrt and the residual sum are 32-bit."""
 
-    def __init__(self, width: int, eps: float, name: str):
+    def __init__(self, width: int, eps: float, name: str, offset: float = 0.0, suffix: str = ".weight"):
+        """`offset`: the multiplier is offset + w (1 for a weight that is stored around zero), added once,
+        in 32-bit, when the weight is bound.  `suffix` completes the tensor's name."""
         self.width, self.eps, self.name = int(width), float(eps), name
+        self.offset, self.tensor = float(offset), name + suffix
 
     def own_weight_specs(self):
-        return [WeightSpec(self.name + ".weight", (self.width,), "norm")]
+        return [WeightSpec(self.tensor, (self.width,), "norm0" if self.offset else "norm")]
 
     def bind_own(self, tensors, rt: Runtime):
-        self.weight = to_f32_vector(tensors[self.name + ".weight"], rt)
+        self.weight = to_f32_vector(tensors[self.tensor], rt)
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()
 
     def weight_bytes(self):
         return self.weight.numel() * 4

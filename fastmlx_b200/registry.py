@@ -3,7 +3,8 @@
 tamnd/fastmlx dispatches on config.json's `model_type` alone through a map of builders
 (compute/models/registry.go:26-128) and names the unknown type in its error.  Here the
 `architectures` strings are keys too, so "llama" and "LlamaForCausalLM" reach the same
-entry.  A new architecture is one `register` call; nothing else in the engine changes.
+entry; a config.json that names its design under `architecture` (one string) is found by
+that.  A new architecture is one `register` call; nothing else in the engine changes.
 """
 from __future__ import annotations
 
@@ -51,7 +52,9 @@ def resolve(config: Mapping) -> Architecture:
     """The architecture that config.json names: `model_type` first, then each entry of
     `architectures`."""
     mt = config.get("model_type")
-    archs = config.get("architectures") or []
+    archs = list(config.get("architectures") or [])
+    if isinstance(config.get("architecture"), str):
+        archs.append(config["architecture"])
     if not mt and not archs:
         raise ConfigError("models: config has no model_type")
     for key in ([mt] if mt else []) + list(archs):

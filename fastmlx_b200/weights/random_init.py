@@ -4,7 +4,9 @@ tamnd/fastmlx has no such mode; its tests fabricate one-element tensors
 (compute/models/llama_forward_test.go:28-39).  Each tensor's values come from a
 generator keyed by (seed, tensor name), so they do not depend on the order in which
 tensors are made or on sharding: matrices, embeddings and biases N(0, 0.02), norm
-weights 1 + N(0, 0.02), drawn in 32-bit and then cast to the stored dtype.
+weights 1 + N(0, 0.02) (N(0, 0.1) where they are stored around zero), convolution taps
+N(0, 0.5), decay rates and their biases such that decays spread over (0, 1), drawn in 32-bit
+and then cast to the stored dtype.
 """
 from __future__ import annotations
 
@@ -28,9 +30,19 @@ def _seed_for(seed: int, name: str) -> int:
 def random_tensor(seed: int, name: str, shape, kind: str, dtype=torch.bfloat16, device="cpu") -> torch.Tensor:
     g = torch.Generator(device=device)
     g.manual_seed(_seed_for(seed, name))
-    t = torch.randn(tuple(shape), generator=g, dtype=torch.float32, device=device) * INIT_STD
-    if kind == "norm":
-        t += 1.0
+    t = torch.randn(tuple(shape), generator=g, dtype=torch.float32, device=device)
+    if kind == "conv":                      # taps of a short convolution: of the order of one
+        t = t * 0.5
+    elif kind == "log_rate":                # the logarithm of a decay rate between about 0.02 and 1
+        t = torch.log(torch.sigmoid(t) * 0.98 + 0.02)
+    elif kind == "rate_bias":
+        t = t * 0.5 - 1.0
+    elif kind == "norm0":                   # a norm weight stored around zero
+        t = t * 0.1
+    else:
+        t = t * INIT_STD
+        if kind == "norm":
+            t += 1.0
     return t.to(dtype)
 
 
