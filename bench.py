@@ -25,6 +25,11 @@ timed; nothing reaches around the scheduler.  One JSON line is printed:
              bytes a decode step reads and the fraction of the copy bandwidth; and a 2,048-token
              prompt whole and in portions of 512
 
+`--designs` leaves all that aside and prints one line of its own: for the layer sizes of Llama-3.2-1B and
+3.1-8B (a few layers each), a Medirax model of equal width, heads and parameter count per layer (three gated
+delta rule layers to one layer of capped sliding-window attention, a dense feed-forward of squared relu) beside
+the Llama layers: a 2,048-token prompt whole and in portions of 512, and steady decoding at batch 8 and 64.
+
 Every timed step reads well over 126 MB (weights alone are 2.5 GB), so no input stays in L2
 between iterations.  tamnd/fastmlx publishes no number to compare with, and cannot run here
 (`--impl reference` says why).
@@ -369,6 +374,63 @@ def shape_block(shape_key: str, block_size: int, pk: dict) -> dict:
 WORK_PROMPT, WORK_GENERATED = 2048, 256
 
 
+# ----------------------------------------------------------------------------- two designs at equal size
+def medirax_like(shape: dict, layers: int, window: int = 1024) -> dict:
+    """A Medirax configuration with a Llama shape's width, heads and vocabulary: layers in the pattern delta,
+    delta, delta, attention; the dense feed-forward has 3/2 of the gated one's hidden size (the same parameters)."""
+    d, nh, nkv, hd = shape["hidden_size"], shape["num_attention_heads"], shape["num_key_value_heads"], shape["head_dim"]
+    mlp = {"kind": "dense", "ff": 3 * shape["intermediate_size"] // 2}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 30.0,
+                     "mask": {"size": window}, "rot": {"dims": hd // 2, "base": 10000.0}}}
+    dl = {"type": "delta", "mlp": mlp, "mixer": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "conv": 4}}
+    return {"architecture": "Medirax", "vocab": shape["vocab_size"], "width": d, "logit_scale": 1.0, "norm": {"eps": 1e-5},
+            "layers": [att if i % 4 == 3 else dl for i in range(layers)]}
+
+
+def design_numbers(cfg: dict, vocab: int, pk: dict, context: int, steps: int, warmup: int) -> dict:
+    """Prefill of 2,048 tokens (whole, in 512s) and steady decoding at batch 8 and 64 behind `context` tokens, through
+    Engine.step(), for one configuration of either design."""
+    import gc
+
+    import torch
+    from fastmlx_b200 import Engine
+    engine = Engine(config=cfg, weights_seed=0, dtype="bfloat16", block_size=16, max_cache_tokens=64 * (context + 64) + 4096,
+                    max_concurrent_requests=64, max_num_batched_tokens=8192, cuda_graphs=True)
+    weight_bytes = engine.model.weight_bytes()
+    out = {"weights_gb": round(weight_bytes / 1e9, 3), "native_executor": engine.step_fn.native is not None}
+    for chunk, key in ((0, "prefill_2048"), (512, "prefill_2048_in_512")):
+        engine.reconfigure(prefill_chunk=chunk)
+        ms = prefill_through_engine(engine, PREFILL_TOKENS, vocab)
+        out[key] = {"ms": round(ms, 3), "tok_s": round(PREFILL_TOKENS / (ms / 1e3), 1)}
+    engine.reconfigure(prefill_chunk=0)
+    state_bytes = sum(2 * e.state[0].numel() * e.state.element_size() for e in engine.manager.entries if e.state is not None)
+    for b in (8, 64):
+        nums = {"weight_bytes": weight_bytes, "kv_bytes_per_token": 0}
+        steady_decode(engine, b, min(context, 512), 8, warmup, vocab, nums, False)              # graphs
+        pt = steady_decode(engine, b, context, steps, warmup, vocab, nums, False)
+        live = type("R", (), {"length": pt["ctx"]})
+        step_bytes = weight_bytes + b * (engine.manager.kv_bytes_read(live) + state_bytes)
+        out[f"decode_b{b}"] = {"ms_per_step": round(pt["ms"], 4), "tok_s": round(b / (pt["ms"] / 1e3), 1),
+                               "gb_per_step": round(step_bytes / 1e9, 3),
+                               "hbm_frac": round(step_bytes / (pt["ms"] / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def compare_designs(shapes, layers: int, context: int, steps: int, warmup: int, pk: dict) -> dict:
+    out = {}
+    for key in shapes:
+        name, shape = SHAPES[key]
+        llama = dict(shape, num_hidden_layers=layers)
+        out[key] = {"layers": layers, "context": context,
+                    "llama": design_numbers(llama, shape["vocab_size"], pk, context, steps, warmup),
+                    "medirax": design_numbers(medirax_like(shape, layers), shape["vocab_size"], pk, context, steps, warmup)}
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -384,6 +446,9 @@ def main() -> int:
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill (for profiling)")
     ap.add_argument("--no-cuda-graphs", action="store_true", help="run decode steps eagerly (for profiling)")
     ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--designs", default="", help="layer sizes (comma-separated, e.g. 1b,8b) at which a Medirax model and the Llama "
+                    "layers of equal size are measured side by side; prints that comparison alone")
+    ap.add_argument("--design-layers", type=int, default=8, help="layers of each model of the --designs comparison")
     ap.add_argument("--only-steps", type=int, default=0,
                     help="for a profiler's launch list: fill the batch, run this many decode steps and stop (no timing, no JSON line)")
     args = ap.parse_args()
@@ -405,6 +470,12 @@ def main() -> int:
     import torch
 
     pk = peaks()
+    if args.designs:
+        keys = [k for k in args.designs.split(",") if k]
+        print(json.dumps({"compare": "medirax beside llama at equal layer sizes", "dtype": "bf16",
+                          "data": "synthetic: seeded uniform-random token ids, random weights", "peaks": pk["source"],
+                          "designs": compare_designs(keys, args.design_layers, min(args.context, 4096), min(steps, 64), warmup, pk)}))
+        return 0
     big = 64 if not args.no_points else args.batch
     pool_tokens = max(big, args.batch) * (args.context + 64) + PREFILL_TOKENS + 64
     engine, cfg, shape_name = build_engine(args.shape, args.layers, pool_tokens, max(big, args.batch), args.block_size,

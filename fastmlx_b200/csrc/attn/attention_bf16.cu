@@ -19,6 +19,13 @@
 //    partials to a workspace, where the block that draws the row's last ticket (or a second kernel) combines
 //    them.  No block spins on a flag: there is nothing to hang.
 //
+// The prefill kernel has a second form for layers whose scores and weights are to be 32-bit (`fmx_attn_prefill_wide`):
+// queries arrive in 32-bit and are split into two bfloat16 terms, q = q1 + q2 with q2 = bf16(q - bf16(q)), so that
+// Q K^T is two products whose sum is taken in the 32-bit accumulator; the probabilities are split the same way for
+// P V.  What the tensor cores see of a query or a weight then has 16 bits of mantissa and every sum is 32-bit.  The
+// scaled scores may be capped, s <- cap * tanh(s / cap), before the softmax; the output's rows may be slices of a
+// wider buffer.  With a window a block walks few tiles, so this form also takes the single-token rows of a step.
+//
 // Keys out of sight (beyond a row's position, before its window, or in no page) are
 // zero-filled in shared memory and masked, never read from the cache.
 #include <mutex>
@@ -179,8 +186,10 @@ __device__ __forceinline__ void load_tiles(bf16* kdst, bf16* vdst, const Cache& 
 }
 
 // S[16 x 8*NT] += Q[16 x HD] . K^T for the key rows [key_row0, key_row0 + 8*NT) of a shared tile.
-template <int NT>
-__device__ __forceinline__ void qk_tile(float (&s)[NT][4], const unsigned (&q)[KSTEPS][4], const bf16* ks, int key_row0) {
+// SPLIT: the queries come as two bfloat16 terms, q and q2; both products land in the same accumulator.
+template <int NT, bool SPLIT = false>
+__device__ __forceinline__ void qk_tile(float (&s)[NT][4], const unsigned (&q)[KSTEPS][4], const bf16* ks, int key_row0,
+                                        const unsigned (*q2)[4] = nullptr) {
   const int lane = threadIdx.x & 31;
   const int mi = lane >> 3, ri = lane & 7;
 #pragma unroll
@@ -193,23 +202,38 @@ __device__ __forceinline__ void qk_tile(float (&s)[NT][4], const unsigned (&q)[K
       ldmatrix_x4(b0, b1, b2, b3, p);
       mma_bf16(s[2 * jp], q[k], b0, b1);
       mma_bf16(s[2 * jp + 1], q[k], b2, b3);
+      if (SPLIT) {
+        mma_bf16(s[2 * jp], q2[k], b0, b1);
+        mma_bf16(s[2 * jp + 1], q2[k], b2, b3);
+      }
     }
   }
 }
 
 // O[16 x HD] += P[16 x 16*KT] . V for the key rows [key_row0, ...) of a shared tile; P comes
 // as the score fragments of 2*KT column tiles.
-template <int KT>
+// what rounding x to bfloat16 leaves behind, itself rounded to bfloat16: x ~ bf16(x) + rest
+__device__ __forceinline__ float bf16_rest(float x) { return x - __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ unsigned pack_bf16_rest(float lo, float hi) { return pack_bf16(bf16_rest(lo), bf16_rest(hi)); }
+
+// SPLIT: P is fed as two bfloat16 terms (its rounding and what the rounding left), so the weights count with 16 bits.
+template <int KT, bool SPLIT = false>
 __device__ __forceinline__ void pv_tile(float (&o)[NT_O][4], const float (&p)[2 * KT][4], const bf16* vs, int key_row0) {
   const int lane = threadIdx.x & 31;
   const int mi = lane >> 3, ri = lane & 7;
 #pragma unroll
   for (int kk = 0; kk < KT; ++kk) {
-    unsigned a[4];
+    unsigned a[4], a2[4];
     a[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
     a[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
     a[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
     a[3] = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+    if (SPLIT) {
+      a2[0] = pack_bf16_rest(p[2 * kk][0], p[2 * kk][1]);
+      a2[1] = pack_bf16_rest(p[2 * kk][2], p[2 * kk][3]);
+      a2[2] = pack_bf16_rest(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+      a2[3] = pack_bf16_rest(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+    }
 #pragma unroll
     for (int np = 0; np < NT_O / 2; ++np) {
       unsigned b0, b1, b2, b3;
@@ -218,6 +242,10 @@ __device__ __forceinline__ void pv_tile(float (&o)[NT_O][4], const float (&p)[2 
       ldmatrix_x4_trans(b0, b1, b2, b3, ptr);
       mma_bf16(o[2 * np], a, b0, b1);
       mma_bf16(o[2 * np + 1], a, b2, b3);
+      if (SPLIT) {
+        mma_bf16(o[2 * np], a2, b0, b1);
+        mma_bf16(o[2 * np + 1], a2, b2, b3);
+      }
     }
   }
 }
@@ -225,9 +253,11 @@ __device__ __forceinline__ void pv_tile(float (&o)[NT_O][4], const float (&p)[2 
 // Mask, then one step of the online softmax over NT column tiles for the two rows (g, g+8)
 // a thread holds.  Scores arrive raw; sl2 = scale * log2(e).  m is kept in the scaled
 // log2 domain.  `lim[x]`, `lo[x]`: last and first visible key of row x.
-template <int NT, bool MASK>
+// CAP: the scaled score is capped first, s <- cap tanh(s scale / cap) (cap_l2 = cap * log2(e), scale_cap = scale / cap).
+template <int NT, bool MASK, bool CAP = false>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&alpha)[2], float sl2,
-                                             int key0, const int (&lim)[2], const int (&lo)[2]) {
+                                             int key0, const int (&lim)[2], const int (&lo)[2], float cap_l2 = 0.f,
+                                             float scale_cap = 0.f) {
   const int t = threadIdx.x & 3;
   float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -236,7 +266,8 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], f
     for (int e = 0; e < 4; ++e) {
       const int x = e >> 1;
       const int key = key0 + 8 * j + 2 * t + (e & 1);
-      const float v = (!MASK || (key <= lim[x] && key >= lo[x])) ? s[j][e] * sl2 : -INFINITY;
+      const float raw = CAP ? cap_l2 * tanhf(s[j][e] * scale_cap) : s[j][e] * sl2;
+      const float v = (!MASK || (key <= lim[x] && key >= lo[x])) ? raw : -INFINITY;
       s[j][e] = v;
       mx[x] = fmaxf(mx[x], v);
     }
@@ -452,11 +483,14 @@ __device__ __forceinline__ void warp_tile_any(bf16* kdst, bf16* vdst, const Cach
 }
 
 // ------------------------------------------------------------------------------------ prefill
+// WIDE: 32-bit queries, two-term products, an optional cap and an output row stride (see the head of the file).
+template <bool WIDE>
 __global__ void __launch_bounds__(THREADS)
-attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kv,
+attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf16* __restrict__ kv,
                     const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ row_start,
                     const int* __restrict__ row_ctx, bf16* __restrict__ out, int nh, int nkv, int page_size,
-                    long long num_pages, float scale, int window, int* status) {
+                    long long num_pages, float scale, int window, int* status, float softcap, long long out_stride,
+                    const int* __restrict__ positions) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   // The last query tiles of a row see the most keys.  Blocks start in the order x, y, z: with the
@@ -467,6 +501,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
   const int n_packed = q_len * rep;
   const int prow0 = tile * BM;
   if (prow0 >= n_packed || ctx < 0) return;
+  if (WIDE && positions != nullptr && positions[t0] < 0) {
+    // a padding row of a captured step (one token at position -1): it sees no key and its output is zero
+    for (int i = threadIdx.x; i < rep * HD; i += THREADS) out[(long long)t0 * out_stride + (long long)g * rep * HD + i] = __float2bfloat16_rn(0.f);
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
   const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages,
                 page_shift_of(page_size)};
@@ -486,14 +525,27 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
   }
   // query fragments, straight from global memory
   unsigned qf[KSTEPS][4];
+  unsigned qf2[WIDE ? KSTEPS : 1][4];
 #pragma unroll
   for (int k = 0; k < KSTEPS; ++k)
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
-      const bf16* qp = q + (long long)(t0 + tok[x]) * q_stride + (long long)head[x] * HD + 16 * k + 2 * tq;
-      qf[k][x] = rvalid[x] ? *reinterpret_cast<const unsigned*>(qp) : 0u;
-      qf[k][x + 2] = rvalid[x] ? *reinterpret_cast<const unsigned*>(qp + 8) : 0u;
+      if (WIDE) {
+        const float* qp = reinterpret_cast<const float*>(q_any) + (long long)(t0 + tok[x]) * q_stride + (long long)head[x] * HD + 16 * k + 2 * tq;
+        const float2 a = rvalid[x] ? *reinterpret_cast<const float2*>(qp) : make_float2(0.f, 0.f);
+        const float2 b = rvalid[x] ? *reinterpret_cast<const float2*>(qp + 8) : make_float2(0.f, 0.f);
+        qf[k][x] = pack_bf16(a.x, a.y);
+        qf[k][x + 2] = pack_bf16(b.x, b.y);
+        qf2[k][x] = pack_bf16_rest(a.x, a.y);
+        qf2[k][x + 2] = pack_bf16_rest(b.x, b.y);
+      } else {
+        const bf16* qp = reinterpret_cast<const bf16*>(q_any) + (long long)(t0 + tok[x]) * q_stride + (long long)head[x] * HD + 16 * k + 2 * tq;
+        qf[k][x] = rvalid[x] ? *reinterpret_cast<const unsigned*>(qp) : 0u;
+        qf[k][x + 2] = rvalid[x] ? *reinterpret_cast<const unsigned*>(qp + 8) : 0u;
+      }
     }
+  const bool capped = WIDE && softcap > 0.f;
+  const float cap_l2 = softcap * LOG2E, scale_cap = capped ? scale / softcap : 0.f;
 
   // keys this block needs: from the first row's window start to the last row's position
   const int first_tok = prow0 / rep;
@@ -538,10 +590,15 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
     for (int j = 0; j < BN / 8; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
-    qk_tile<BN / 8>(s, qf, ks, 0);
+    qk_tile<BN / 8, WIDE>(s, qf, ks, 0, qf2);
     float alpha[2];
     const int tk0 = kstart + it * BN;
-    if (warp_full && tk0 >= sure_lo && tk0 + BN - 1 <= sure_hi)
+    const bool open = warp_full && tk0 >= sure_lo && tk0 + BN - 1 <= sure_hi;
+    if (capped && open)
+      softmax_step<BN / 8, false, true>(s, m, l, alpha, sl2, tk0, lim, lo, cap_l2, scale_cap);
+    else if (capped)
+      softmax_step<BN / 8, true, true>(s, m, l, alpha, sl2, tk0, lim, lo, cap_l2, scale_cap);
+    else if (open)
       softmax_step<BN / 8, false>(s, m, l, alpha, sl2, tk0, lim, lo);
     else
       softmax_step<BN / 8, true>(s, m, l, alpha, sl2, tk0, lim, lo);
@@ -550,7 +607,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
       o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
       o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
     }
-    pv_tile<BN / 16>(o, s, vs, 0);
+    pv_tile<BN / 16, WIDE>(o, s, vs, 0);
   }
   cp_async_wait<0>();
 #pragma unroll
@@ -559,7 +616,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
     l[x] += __shfl_xor_sync(0xffffffffu, l[x], 2);
     if (!rvalid[x]) continue;
     const float inv = l[x] > 0.f ? 1.0f / l[x] : 0.f;
-    bf16* op = out + ((long long)(t0 + tok[x]) * nh + head[x]) * HD + 2 * tq;
+    bf16* op = out + (long long)(t0 + tok[x]) * out_stride + (long long)head[x] * HD + 2 * tq;
 #pragma unroll
     for (int n = 0; n < NT_O; ++n)
       *reinterpret_cast<unsigned*>(op + 8 * n) = pack_bf16(o[n][2 * x] * inv, o[n][2 * x + 1] * inv);
@@ -1066,7 +1123,7 @@ FMX_EXPORT int fmx_attn_prefill(const void* q, long long q_stride, const void* k
   if (rows > 65535 || nkv > 65535) return fmx_fail("fmx_attn_prefill: too many rows or kv heads for one launch");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)prefill_smem());
     if (e != cudaSuccess) return fmx_fail("fmx_attn_prefill: shared memory of %zu bytes refused: %s", prefill_smem(),
                                           cudaGetErrorString(e));
@@ -1076,9 +1133,42 @@ FMX_EXPORT int fmx_attn_prefill(const void* q, long long q_stride, const void* k
   const long long tiles = ((long long)max_q_len * rep + BM - 1) / BM;
   if (tiles > 65535) return fmx_fail("fmx_attn_prefill: %d query tokens in one row are too many for one launch", max_q_len);
   dim3 grid(nkv, rows, (unsigned)tiles);
-  attn_prefill_kernel<<<grid, THREADS, prefill_smem(), stream>>>(
-      (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv,
-      page_size, num_pages, scale, window, status);
+  attn_prefill_kernel<false><<<grid, THREADS, prefill_smem(), stream>>>(
+      q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv,
+      page_size, num_pages, scale, window, status, 0.f, (long long)nh * HD, (const int*)nullptr);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
+// The form with 32-bit queries q[T, nh*hd] (row stride in floats), two-term products, capped scores (softcap > 0)
+// and an output whose rows are `out_stride` elements apart.  Takes every kind of row, single tokens included.
+// positions (or null): the step's token positions; a row whose first token stands at -1 is padding and gets zeros.
+FMX_EXPORT int fmx_attn_prefill_wide(const float* q, long long q_stride, const void* kv, const int* block_tables,
+                                     int bt_stride, const int* row_start, const int* row_ctx, const int* positions, void* out,
+                                     long long out_stride, int rows, int max_q_len, int nh, int nkv, int page_size,
+                                     long long num_pages, float scale, float softcap, int window, int* status,
+                                     cudaStream_t stream) {
+  if (rows == 0 || max_q_len == 0) return 0;
+  if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0)
+    return fmx_fail("fmx_attn_prefill_wide: bad sizes rows=%d nh=%d nkv=%d page=%d", rows, nh, nkv, page_size);
+  if (rows > 65535 || nkv > 65535) return fmx_fail("fmx_attn_prefill_wide: too many rows or kv heads for one launch");
+  if (q_stride % 2 || ((uintptr_t)q & 7) || out_stride % 2 || ((uintptr_t)out & 3) || out_stride < (long long)nh * HD)
+    return fmx_fail("fmx_attn_prefill_wide: queries in 8-byte pairs and outputs in 4-byte pairs, rows at least nh*hd wide");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)prefill_smem());
+    if (e != cudaSuccess) return fmx_fail("fmx_attn_prefill_wide: shared memory of %zu bytes refused: %s", prefill_smem(),
+                                          cudaGetErrorString(e));
+    configured = true;
+  }
+  const int rep = nh / nkv;
+  const long long tiles = ((long long)max_q_len * rep + BM - 1) / BM;
+  if (tiles > 65535) return fmx_fail("fmx_attn_prefill_wide: %d query tokens in one row are too many for one launch", max_q_len);
+  dim3 grid(nkv, rows, (unsigned)tiles);
+  attn_prefill_kernel<true><<<grid, THREADS, prefill_smem(), stream>>>(
+      q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size,
+      num_pages, scale, window, status, softcap, out_stride, positions);
   FMX_LAUNCH_CHECK();
   return 0;
 }

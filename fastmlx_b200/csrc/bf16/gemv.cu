@@ -13,7 +13,8 @@
 // SM streaming, where 16-row tiles had to split K over blocks and reduce through L2.
 //
 // Epilogues: bias; residual add (in place when out is the residual); SiLU(gate) * up for a
-// weight whose rows alternate in blocks of `blk` gate rows and their `blk` up rows.
+// weight whose rows alternate in blocks of `blk` gate rows and their `blk` up rows; an
+// activation of the product (blk = -1: relu(x)^2, -2: gelu in its tanh form, -3: silu).
 #include "common.cuh"
 
 namespace {
@@ -178,6 +179,12 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
       v = gte / (1.0f + expf(-gte)) * bf16r(up);
     }
     if (bias != nullptr) v += bias[n];
+    if (!DUAL && blk < 0) {                         // as the unfused path rounds: the product first, then its activation
+      const float z = bf16r(v);
+      if (blk == -1) { const float p = fmaxf(z, 0.f); v = p * p; }
+      else if (blk == -2) v = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+      else v = z / (1.0f + expf(-z));
+    }
     if (residual != nullptr) v = bf16r(v) + __bfloat162float(residual[(long long)tok * ldr + n]);
     store_out<TO>(out + (long long)tok * ldo + n, v);
   }
@@ -261,7 +268,7 @@ FMX_EXPORT int fmx_gemv_plan_warps(int n_out, int K, int wide, int sms) {
 // x [M <= 16, K] and W [N, K] bfloat16, rows 16-byte aligned; out [M, N] bfloat16 (out_dtype 1)
 // or float (0); bias float[N] or null; residual bfloat16 [M, n_out] or null (may be `out`).
 // blk > 0: W's rows alternate in blocks of blk gate rows and blk up rows, out is [M, N/2] =
-// silu(gate) * up in bfloat16.  wide: 8, 16 or 32 output features per block; warps: 8 or 16
+// silu(gate) * up in bfloat16.  blk < 0: out = act(product + bias) in bfloat16, act = relu^2 (-1), gelu-tanh (-2), silu (-3).  wide: 8, 16 or 32 output features per block; warps: 8 or 16
 // per block (16 when few blocks must keep many bytes in flight over a long K).
 FMX_EXPORT int fmx_gemv(const void* x, long long ldx, const void* W, long long ldw, const float* bias, const void* residual,
                         long long ldr, void* out, long long ldo, int M, int N, int K, int out_dtype, int blk, int wide,
@@ -270,12 +277,13 @@ FMX_EXPORT int fmx_gemv(const void* x, long long ldx, const void* W, long long l
   if (M < 0 || M > 16 || N < 0 || K <= 0) return fmx_fail("fmx_gemv: takes 1..16 rows, got M=%d N=%d K=%d", M, N, K);
   if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15))
     return fmx_fail("fmx_gemv: rows must be 16-byte aligned (K=%d ldx=%lld ldw=%lld)", K, ldx, ldw);
-  if (blk < 0 || (blk > 0 && (blk % 16 || N % (2 * blk))))
+  if (blk < -3 || (blk > 0 && (blk % 16 || N % (2 * blk))))
     return fmx_fail("fmx_gemv: gate/up blocks of %d do not tile %d rows", blk, N);
+  if (blk < 0 && out_dtype != FMX_BF16) return fmx_fail("fmx_gemv: an activation epilogue writes bfloat16");
   if (blk > 0 && out_dtype != FMX_BF16) return fmx_fail("fmx_gemv: the SiLU-mul epilogue writes bfloat16");
   const bool hi = M > 8;
   const int n_out = blk > 0 ? N / 2 : N;
-  if (wide == 0) wide = fmx_gemv_plan_width(n_out, blk, 0);
+  if (wide == 0) wide = fmx_gemv_plan_width(n_out, blk > 0 ? blk : 0, 0);
   if (warps == 0) warps = fmx_gemv_plan_warps(n_out, K, wide, 0);
   if (warps != 8 && warps != 16) return fmx_fail("fmx_gemv: 8 or 16 warps per block, not %d", warps);
   if (warps == 16 && wide == 32) return fmx_fail("fmx_gemv: 32 features per block go with 8 warps");

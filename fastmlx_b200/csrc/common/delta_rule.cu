@@ -13,8 +13,9 @@
 //                     (q also times D^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)).
 //   conv_state_update per request: the last taps-1 inputs of the portion replace the convolution state.
 //   delta_rule        the recurrence.  Columns of S are independent (column j needs v_j only), so a column is
-//                     given to 8 adjacent lanes that hold D/8 of its values each in registers; the tokens of a
-//                     request's portion are walked in order, the next token's operands loaded a token ahead.
+//                     given to 2 to 8 adjacent lanes that hold 16 (or 32) of its values each in registers; the
+//                     tokens of a request's portion are walked in order, their operands staged through shared
+//                     memory a run of tokens ahead.
 //   gated_rmsnorm     o of each head divided by its root mean square, times a weight, times SiLU(gate).
 //
 // A slot's state is one run of 32-bit floats: S^T of every head, [H, Dv, D], and then the convolution inputs,
@@ -113,16 +114,29 @@ __global__ void conv_state_update_kernel(const T* proj, long long stride, const 
     if (j < taps - 1) cs[(long long)j * C + c] = keep[j];
 }
 
-// grid (ceil(Dv / 16), H, R), 128 threads: 16 columns of S, 8 lanes each; lane `sub` of a column holds rows
-// d = sub * NPL + i, i < NPL (D <= 8 NPL).  qkv [T, C] and gb [T, 2H] as delta_prepare left them; out [T, H*Dv].
-template <int NPL>
+// grid (ceil(Dv / COLS), H, R), 128 threads: COLS = 128 / L columns of S, L adjacent lanes each; lane `sub` of a
+// column holds rows d = sub * NPL + i, i < NPL (D <= L NPL).  qkv [T, C] and gb [T, 2H] as delta_prepare left them;
+// out [T, H*Dv].  The walk over a request's tokens is one chain of dependent steps per column (decay, dot with k over
+// the lanes, write, dot with q), so what matters is the length of a step: a token's operands (k and q of the head's
+// group, the block's values, decay and beta) come through shared memory in runs of TB tokens, the next run copied
+// (cp.async) while the current one is walked, and the dots run in four interleaved sums.
+template <int NPL, int L, int TB>
 __global__ void __launch_bounds__(128)
 delta_rule_kernel(const float* qkv, const float* gb, const int* row_start, const int* row_slot, float* state,
                   long long slot_stride, float* out, int H, int G, int D, int Dv, int max_slots) {
+  constexpr int COLS = 128 / L, DP = NPL * L;
+  constexpr int ROWF = (2 * DP + COLS + 2 + 3) / 4 * 4;       // floats of one token in a run: k | q | values | decay, beta
+  extern __shared__ __align__(16) float runs[];                // two runs of TB tokens
+  const int r = blockIdx.z, h = blockIdx.y;
+  const int c0 = blockIdx.x * COLS;
+  const int col = c0 + (threadIdx.x / L), sub = threadIdx.x % L;
+  if (D < DP)                                    // rows d >= D of k and q are zero and stay so
+    for (int i = threadIdx.x; i < 2 * TB * 2 * (DP - D); i += 128) {
+      const int s = i / (2 * (DP - D)), e = i - s * 2 * (DP - D);
+      runs[s * ROWF + (e < DP - D ? D + e : DP + D + e - (DP - D))] = 0.f;
+    }
   pdl_wait();
   pdl_trigger();
-  const int r = blockIdx.z, h = blockIdx.y;
-  const int col = blockIdx.x * 16 + (threadIdx.x >> 3), sub = threadIdx.x & 7;
   const int slot = row_slot[r];
   if (slot < 0 || slot >= max_slots) return;
   const int first = row_start[r], n = row_start[r + 1] - first;
@@ -131,53 +145,89 @@ delta_rule_kernel(const float* qkv, const float* gb, const int* row_start, const
   const bool live = col < Dv;
   const int colc = live ? col : Dv - 1;          // lanes beyond the last column follow it and write nothing
   float* sp = state + (long long)slot * slot_stride + ((long long)h * Dv + colc) * D;
-  float S[NPL], k[NPL], q[NPL], kn[NPL], qn[NPL];
+  float S[NPL], k[NPL], q[NPL];
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
     const int d = sub * NPL + i;
     S[i] = d < D ? sp[d] : 0.f;
   }
-  const long long qoff = (long long)g * D, koff = (long long)(G + g) * D, voff = (long long)2 * G * D + (long long)h * Dv + colc;
-  float vn = 0.f, gn = 0.f, bn = 0.f;
-  auto load = [&](int tok) {
-    const float* p = qkv + (long long)tok * C;
-#pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      const int d = sub * NPL + i;
-      kn[i] = d < D ? p[koff + d] : 0.f;
-      qn[i] = d < D ? p[qoff + d] : 0.f;
-    }
-    vn = p[voff];
-    gn = gb[(long long)tok * 2 * H + h];
-    bn = gb[(long long)tok * 2 * H + H + h];
+  const long long qoff = (long long)g * D, koff = (long long)(G + g) * D, voff = (long long)2 * G * D + (long long)h * Dv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // 16-byte copies where a token's k and q start on 16 bytes in global memory, else 4-byte ones
+  const bool wide = (D & 3) == 0 && (C & 3) == 0 && (((uintptr_t)qkv) & 15) == 0;
+  auto cp = [](float* dst, const float* src, int bytes) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(dst);
+    if (bytes == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(src));
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(sa), "l"(src));
   };
-  if (n > 0) load(first);
-  for (int i0 = 0; i0 < n; ++i0) {
-    const int tok = first + i0;
-#pragma unroll
-    for (int i = 0; i < NPL; ++i) { k[i] = kn[i]; q[i] = qn[i]; }
-    const float v = vn, gd = gn, beta = bn;
-    if (i0 + 1 < n) load(tok + 1);
-    float dot = 0.f;
-#pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      S[i] *= gd;
-      dot = fmaf(S[i], k[i], dot);
+  auto copy_run = [&](int run) {                 // tokens [run * TB, ...) of the request into buffer run & 1: a warp per token
+    float* dst0 = runs + (run & 1) * TB * ROWF;
+    const int t0 = run * TB, cnt = min(TB, n - t0);
+    for (int s = warp; s < cnt; s += 4) {
+      const float* row = qkv + (long long)(first + t0 + s) * C;
+      float* dst = dst0 + s * ROWF;
+      if (wide) {
+        for (int d = 4 * lane; d < D; d += 128) {
+          cp(dst + d, row + koff + d, 16);
+          cp(dst + DP + d, row + qoff + d, 16);
+        }
+      } else {
+        for (int d = lane; d < D; d += 32) {
+          cp(dst + d, row + koff + d, 4);
+          cp(dst + DP + d, row + qoff + d, 4);
+        }
+      }
+      for (int e = lane; e < COLS; e += 32) cp(dst + 2 * DP + e, row + voff + min(c0 + e, Dv - 1), 4);
+      if (lane < 2) cp(dst + 2 * DP + COLS + lane, gb + (long long)(first + t0 + s) * 2 * H + lane * H + h, 4);   // decay, beta
     }
-    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-    const float u = beta * (v - dot);
-    float o = 0.f;
-#pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      S[i] = fmaf(k[i], u, S[i]);
-      o = fmaf(S[i], q[i], o);
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  const int n_runs = (n + TB - 1) / TB;
+  __syncthreads();                               // the zeros are written before any copy lands
+  if (n_runs > 0) copy_run(0);
+  for (int run = 0; run < n_runs; ++run) {
+    if (run + 1 < n_runs) {
+      copy_run(run + 1);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
     }
-    o += __shfl_xor_sync(0xffffffffu, o, 1);
-    o += __shfl_xor_sync(0xffffffffu, o, 2);
-    o += __shfl_xor_sync(0xffffffffu, o, 4);
-    if (live && sub == 0) out[(long long)tok * H * Dv + (long long)h * Dv + col] = o;
+    __syncthreads();
+    const float* buf = runs + (run & 1) * TB * ROWF;
+    const int cnt = min(TB, n - run * TB);
+#pragma unroll 2
+    for (int s = 0; s < cnt; ++s) {
+      const float* tokp = buf + s * ROWF;
+#pragma unroll
+      for (int i = 0; i < NPL; i += 4) {           // 16-byte loads: a run's rows and a lane's share start on 16 bytes
+        const float4 k4 = *reinterpret_cast<const float4*>(tokp + sub * NPL + i);
+        const float4 q4 = *reinterpret_cast<const float4*>(tokp + DP + sub * NPL + i);
+        k[i] = k4.x; k[i + 1] = k4.y; k[i + 2] = k4.z; k[i + 3] = k4.w;
+        q[i] = q4.x; q[i + 1] = q4.y; q[i + 2] = q4.z; q[i + 3] = q4.w;
+      }
+      const float v = tokp[2 * DP + (threadIdx.x / L)], gd = tokp[2 * DP + COLS], beta = tokp[2 * DP + COLS + 1];
+      float dp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        S[i] *= gd;
+        dp[i & 3] = fmaf(S[i], k[i], dp[i & 3]);
+      }
+      float dot = (dp[0] + dp[1]) + (dp[2] + dp[3]);
+#pragma unroll
+      for (int o = 1; o < L; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = beta * (v - dot);
+      float op[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        S[i] = fmaf(k[i], u, S[i]);
+        op[i & 3] = fmaf(S[i], q[i], op[i & 3]);
+      }
+      float o = (op[0] + op[1]) + (op[2] + op[3]);
+#pragma unroll
+      for (int x = 1; x < L; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+      if (live && sub == 0) out[(long long)(first + run * TB + s) * H * Dv + (long long)h * Dv + col] = o;
+    }
+    __syncthreads();                             // the run is walked: its buffer may take the run after the next
   }
   if (live) {
 #pragma unroll
@@ -245,20 +295,35 @@ FMX_EXPORT int fmx_delta_prepare(const void* proj, long long stride, const float
 
 FMX_EXPORT int fmx_delta_rule(const float* qkv, const float* gb, const int* row_start, const int* row_slot, float* state,
                               long long slot_stride, float* out, int R, int H, int G, int D, int Dv, int max_slots,
-                              cudaStream_t stream) {
+                              int lanes, cudaStream_t stream) {
   if (R == 0) return 0;
   if (R < 0 || H <= 0 || G <= 0 || H % G || D <= 0 || Dv <= 0 || D > 256)
     return fmx_fail("fmx_delta_rule: bad sizes R=%d H=%d G=%d D=%d Dv=%d", R, H, G, D, Dv);
   if (H > 65535 || R > 65535) return fmx_fail("fmx_delta_rule: batch too large");
-  const dim3 grid((Dv + 15) / 16, H, R), block(128);
-#define FMX_DELTA_RULE(NPL)                                                                                            \
-  fmx_launch(delta_rule_kernel<NPL>, grid, block, 0, stream, qkv, gb, row_start, row_slot, state, slot_stride, out, H, \
-             G, D, Dv, max_slots)
-  if (D <= 16) FMX_DELTA_RULE(2);
-  else if (D <= 32) FMX_DELTA_RULE(4);
-  else if (D <= 64) FMX_DELTA_RULE(8);
-  else if (D <= 128) FMX_DELTA_RULE(16);
-  else FMX_DELTA_RULE(32);
+#define FMX_DELTA_RULE(NPL, L, TB)                                                                                     \
+  do {                                                                                                                 \
+    constexpr int cols = 128 / (L), rowf = (2 * (NPL) * (L) + cols + 2 + 3) / 4 * 4;                                   \
+    const dim3 grid((Dv + cols - 1) / cols, H, R);                                                                     \
+    fmx_launch(delta_rule_kernel<NPL, L, TB>, grid, dim3(128), (size_t)2 * (TB) * rowf * sizeof(float), stream, qkv, gb, \
+               row_start, row_slot, state, slot_stride, out, H, G, D, Dv, max_slots);                                  \
+  } while (0)
+  // Lanes per column: few lanes make a step's sums over lanes short, many lanes make its dots short and give the
+  // grid more warps.  `lanes` = 0 leaves the choice here.
+  if (lanes == 0) lanes = 8;
+  if (lanes != 2 && lanes != 4 && lanes != 8) return fmx_fail("fmx_delta_rule: 2, 4 or 8 lanes per column, not %d", lanes);
+  const int per_lane = (D + lanes - 1) / lanes;
+  if (per_lane > 32) return fmx_fail("fmx_delta_rule: %d rows of state are too many for %d lanes per column", D, lanes);
+#define FMX_DELTA_LANES(L)                      \
+  do {                                          \
+    if (per_lane <= 4) FMX_DELTA_RULE(4, L, 16);       \
+    else if (per_lane <= 8) FMX_DELTA_RULE(8, L, 16);  \
+    else if (per_lane <= 16) FMX_DELTA_RULE(16, L, 16); \
+    else FMX_DELTA_RULE(32, L, 8);              \
+  } while (0)
+  if (lanes == 2) FMX_DELTA_LANES(2);
+  else if (lanes == 4) FMX_DELTA_LANES(4);
+  else FMX_DELTA_LANES(8);
+#undef FMX_DELTA_LANES
 #undef FMX_DELTA_RULE
   FMX_LAUNCH_CHECK();
   return 0;

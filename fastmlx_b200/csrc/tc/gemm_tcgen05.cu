@@ -35,7 +35,7 @@ using namespace fmx_tc;
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
 
-enum Epilogue { EPI_PLAIN = 0, EPI_SILU_MUL = 1, EPI_RESIDUAL = 2 };
+enum Epilogue { EPI_PLAIN = 0, EPI_SILU_MUL = 1, EPI_RESIDUAL = 2, EPI_RELU2 = 3 };   // RELU2: max(x, 0)^2
 
 template <int BN> struct Cfg {
   static constexpr int STAGES = BN == 256 ? 4 : (BN == 192 ? 5 : 6);
@@ -208,6 +208,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               const float w = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[i])));
               f[i] = silu(g) * w;
             }
+            if (EPI == EPI_RELU2) {
+              // as the unfused path rounds: the product to bfloat16 first, then the square of its positive part
+              const float p = fmaxf(__bfloat162float(__float2bfloat16_rn(f[i])), 0.f);
+              f[i] = p * p;
+            }
           }
           const int col = out_n0 + c;
           bf16* dst = C + (long long)row * ldc + col;
@@ -322,6 +327,9 @@ FMX_EXPORT int fmx_gemm_tcgen05(const void* A, long long lda, const void* W, lon
   FMX_TC_CASE(128, EPI_SILU_MUL);
   FMX_TC_CASE(256, EPI_RESIDUAL);
   FMX_TC_CASE(128, EPI_RESIDUAL);
+  FMX_TC_CASE(256, EPI_RELU2);
+  FMX_TC_CASE(192, EPI_RELU2);
+  FMX_TC_CASE(128, EPI_RELU2);
 #undef FMX_TC_CASE
   return fmx_fail("fmx_gemm_tcgen05: no kernel for tile width %d, epilogue %d", bn, epilogue);
 }

@@ -162,7 +162,7 @@ GEMV_MAX_ROWS = 16
 LIBRARY_MIN_FEATURES = 65536     # from this many output features on (the vocabulary) the library's product streams best
 TC_MIN_ROWS = 128
 GATE_UP_BLOCK = 128              # gate/up rows of a fused weight alternate in blocks of this many
-EPI_PLAIN, EPI_SILU_MUL, EPI_RESIDUAL = 0, 1, 2
+EPI_PLAIN, EPI_SILU_MUL, EPI_RESIDUAL, EPI_RELU2 = 0, 1, 2, 3
 
 
 def _bf16_operands(x, w) -> bool:
@@ -177,14 +177,19 @@ def can_gemv(x, w) -> bool:
     return _bf16_operands(x, w) and x.shape[0] <= GEMV_MAX_ROWS
 
 
-def gemv(x, w, bias=None, out_dtype=torch.bfloat16, residual=None, block: int = 0, out=None, wide=None, warps=None):
+def gemv(x, w, bias=None, out_dtype=torch.bfloat16, residual=None, block: int = 0, out=None, wide=None, warps=None,
+         act: str | None = None):
     """x[M <= 16, K] @ w[N, K]^T, one block per `wide` (8, 16, 32) output features and the whole of K:
     nothing is summed across blocks.  residual [M, n_out] is added to the product (out may be
     the residual itself).  block > 0: w's rows alternate in blocks of `block` gate rows and
-    their up rows, and the result is silu(gate) * up, [M, N/2]."""
+    their up rows, and the result is silu(gate) * up, [M, N/2].  act (relu2, gelu_tanh, silu): the
+    activation of the product (and bias), in the same pass; `out` may be a slice of a wider buffer."""
     M, K = x.shape
     N = w.shape[0]
     n_out = N // 2 if block else N
+    if act is not None:
+        assert not block and out_dtype == torch.bfloat16
+        block = -1 - ACTIVATIONS[act]
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     # wide / warps left open: the library plans them (`fmx_gemv_plan_width`, `fmx_gemv_plan_warps`)
@@ -255,14 +260,17 @@ def can_tc(x, w, bias=None, out_dtype=torch.bfloat16, epilogue: int = EPI_PLAIN)
             and tc_fills_the_gpu(x.shape[0], w.shape[0], num_sms(x.device)))
 
 
-def gemm_tcgen05(x, w, status=None, epilogue: int = EPI_PLAIN, residual=None, bn: int | None = None) -> torch.Tensor:
+def gemm_tcgen05(x, w, status=None, epilogue: int = EPI_PLAIN, residual=None, bn: int | None = None, out=None) -> torch.Tensor:
     """x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory).
     epilogue EPI_SILU_MUL: w's rows come in blocks of bn/2 gate rows then bn/2 up rows, and the
-    result is silu(gate) * up, [M, N/2]; EPI_RESIDUAL: residual + product."""
+    result is silu(gate) * up, [M, N/2]; EPI_RESIDUAL: residual + product; EPI_RELU2: the square of the
+    product's positive part.  `out` may be a slice of a wider buffer."""
     M, K = x.shape
     N = w.shape[0]
     sms = num_sms(x.device)
-    out = torch.empty((M, N // 2 if epilogue == EPI_SILU_MUL else N), dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        out = torch.empty((M, N // 2 if epilogue == EPI_SILU_MUL else N), dtype=torch.bfloat16, device=x.device)
+    assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape == (M, N // 2 if epilogue == EPI_SILU_MUL else N)
     call("tc", "fmx_gemm_tcgen05", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
          _ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, int(bn or 0), epilogue, sms,
          _ptr(status if status is not None else _status_word(x.device)), _stream())
@@ -352,6 +360,29 @@ def paged_attention_general(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, 
     return out
 
 
+def wide_attention_ok(q, kv, hd, vd) -> bool:
+    """Does the tiled tensor-core kernel with two-term products take this attention?  bfloat16 pages in the common
+    layout (values as wide as keys), a head size in steps of 16 up to 256, 32-bit queries in 8-byte pairs."""
+    return (kv is not None and kv.dtype == torch.bfloat16 and kv.dim() == 5 and q.dtype == torch.float32 and hd == vd
+            and hd % 16 == 0 and hd <= 256 and q.stride(0) % 2 == 0 and q.data_ptr() % 8 == 0)
+
+
+def paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out=None) -> torch.Tensor:
+    """Attention of any mix of rows on the tensor cores with 32-bit scores and weights: the 32-bit queries
+    q[T, nh*hd] and the probabilities enter the products as two bfloat16 terms each, sums are 32-bit, scores may be
+    capped (softcap > 0).  `out` may be a slice of a wider buffer.  -> [T, nh*hd] in bfloat16."""
+    T = q.shape[0]
+    if out is None:
+        out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=q.device)
+    assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
+    bt = group.block_tables
+    call(f"attn_hd{hd}", "fmx_attn_prefill_wide", q.data_ptr(), q.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
+         ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), out.stride(0), ctx.R,
+         int(ctx.max_q_len), nh, nkv, kv.shape[3], kv.shape[0], float(scale), float(softcap or 0.0), int(window),
+         _ptr(ctx.status), _stream())
+    return out
+
+
 # ----------------------------------------------------------------------------- gated delta rule
 def delta_prepare(proj, ab, conv_w, a_log, dt_bias, ctx, state, conv_off, H, G, D, Dv, taps):
     """What the recurrence of a gated delta rule layer takes in, from the projections of a step:
@@ -374,14 +405,15 @@ def delta_prepare(proj, ab, conv_w, a_log, dt_bias, ctx, state, conv_off, H, G, 
     return qkv, gb
 
 
-def delta_rule(qkv, gb, ctx, state, H, G, D, Dv) -> torch.Tensor:
+def delta_rule(qkv, gb, ctx, state, H, G, D, Dv, lanes: int = 0) -> torch.Tensor:
     """The gated delta rule over every request's tokens of the step, in order, from and into the requests'
     state slots (S^T per head, [H, Dv, D], at the head of a slot): S <- g S; u = beta (v - S^T k);
-    S <- S + k u^T; o = S^T q.  -> o in 32-bit, [T, H*Dv]."""
+    S <- S + k u^T; o = S^T q.  `lanes` (2, 4, 8; 0: the library's choice): lanes that share a column of S.
+    -> o in 32-bit, [T, H*Dv]."""
     T = qkv.shape[0]
     out = torch.empty((T, H * Dv), dtype=torch.float32, device=qkv.device)
     call("common", "fmx_delta_rule", qkv.data_ptr(), gb.data_ptr(), ctx.row_start.data_ptr(), ctx.row_slot.data_ptr(),
-         state.data_ptr(), state.stride(0), out.data_ptr(), ctx.R, H, G, D, Dv, state.shape[0], _stream())
+         state.data_ptr(), state.stride(0), out.data_ptr(), ctx.R, H, G, D, Dv, state.shape[0], int(lanes), _stream())
     return out
 
 

@@ -37,7 +37,7 @@ _SIGNATURES = {
         "fmx_qk_prepare": [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _L, _I, _P, _P],
         "fmx_delta_prepare": [_P, _L, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
                               _P, _P],
-        "fmx_delta_rule": [_P, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _I, _P],
+        "fmx_delta_rule": [_P, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "fmx_gated_rmsnorm": [_P, _P, _L, _P, _P, _L, _I, _I, _I, _F, _I, _P],
         "fmx_activation": [_P, _L, _P, _L, _I, _I, _I, _I, _P],
     },
@@ -51,6 +51,7 @@ _SIGNATURES = {
     "attn": {
         "fmx_attn_prefill_tc": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _I, _P, _L, _P],
         "fmx_attn_prefill": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],
+        "fmx_attn_prefill_wide": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _L, _F, _F, _I, _P, _P],
         "fmx_attn_decode": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P, _I, _I, _I, _P],
     },
 }

@@ -79,6 +79,12 @@ class GQAAttention(Mixer):
         store = cache.writable and not self.share_kv
         q = k.qk_prepare(qkv, ctx.positions, inv_freq, rot, trad, self.qk_norm_eps, g.slot_mapping if store else None,
                          cache.kv if store else None, self.nh, self.nkv, self.hd, self.vd, ctx.status)
+        wide = getattr(k, "wide_attention_ok", None)
+        if wide is not None and wide(q, cache.kv, self.hd, self.vd) and (out is None or (out.stride(0) % 2 == 0
+                                                                                         and out.data_ptr() % 4 == 0)):
+            # bfloat16 pages: the tiled tensor-core kernel, queries and weights as two bfloat16 terms each
+            return k.paged_attention_wide(q, cache.kv, ctx, g, self.nh, self.nkv, self.hd, self.scale, self.softcap,
+                                          self.window, out=out)
         return k.paged_attention_general(q, cache.kv, ctx, g, self.nh, self.nkv, self.hd, self.vd, self.scale,
                                          self.softcap, self.window, g.page_size, out=out)
 

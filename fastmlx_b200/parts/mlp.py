@@ -77,7 +77,14 @@ class DenseMLP(FeedForward):
 
     def forward_inner(self, x, ctx, out=None):
         """The hidden layer after its activation, [T, intermediate]; into `out` where one is given."""
-        return self.rt.k.activation(self.up.forward(x), self.activation, out=out)
+        k, w, b = self.rt.k, self.up.weight, self.up.bias
+        if hasattr(k, "can_gemv") and k.can_gemv(x, w) and (out is None or out.dtype == torch.bfloat16):
+            # decode steps: the activation in the product's epilogue
+            return k.gemv(x, w, b, act=self.activation, out=out)
+        if self.activation == "relu2" and b is None and hasattr(k, "can_tc") and k.can_tc(x, w, None, x.dtype, k.EPI_RELU2):
+            # prompt portions: the same on the tensor-memory kernel
+            return k.gemm_tcgen05(x, w, ctx.status if ctx is not None else None, epilogue=k.EPI_RELU2, out=out)
+        return k.activation(self.up.forward(x), self.activation, out=out)
 
     def forward(self, x, ctx):
         return self.down.forward(self.forward_inner(x, ctx))

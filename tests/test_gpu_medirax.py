@@ -232,7 +232,7 @@ def test_gated_norm_and_activations(dtype):
 
 
 def _attention_case(window, cap, lens_by_step, standout, hd=16, vd=24, nh=4, nkv=2, page=16, dtype=torch.float32,
-                    rot=0, norm_eps=None):
+                    rot=0, norm_eps=None, wide=False):
     """Requests fed in the given portions through the cache manager and the two attention kernels; the query at
     position p of request 0 is aligned with the key at `standout(p)` so strongly that, where that key is seen, the
     output is its value.  -> (outputs per request [n, nh*vd], plain outputs)."""
@@ -293,7 +293,14 @@ def _attention_case(window, cap, lens_by_step, standout, hd=16, vd=24, nh=4, nkv
                                     seqs[r][2][at[r]:at[r] + n].reshape(n, -1)], 1) for r, n in live]).to(dev).contiguous()
         grp = ctx.groups[0]
         q32 = k.qk_prepare(qkv, ctx.positions, inv_freq, rot, False, norm_eps, grp.slot_mapping, m.entries[0].kv, nh, nkv, hd, vd, status)
-        out = k.paged_attention_general(q32, m.entries[0].kv, ctx, grp, nh, nkv, hd, vd, scale, cap, window, page).cpu().double()
+        if wide:                                     # the tiled tensor-core kernel with two-term products
+            assert k.wide_attention_ok(q32, m.entries[0].kv, hd, vd)
+            joined = torch.zeros((q32.shape[0], nh * vd + 6), dtype=dtype, device=dev)
+            out = k.paged_attention_wide(q32, m.entries[0].kv, ctx, grp, nh, nkv, hd, scale, cap, window, out=joined[:, 2:2 + nh * vd])
+            assert joined[:, :2].abs().max().item() == 0 and joined[:, 2 + nh * vd:].abs().max().item() == 0
+            out = out.cpu().double()
+        else:
+            out = k.paged_attention_general(q32, m.entries[0].kv, ctx, grp, nh, nkv, hd, vd, scale, cap, window, page).cpu().double()
         off = 0
         for r, n in live:
             got[r].append(out[off:off + n])
@@ -305,17 +312,22 @@ def _attention_case(window, cap, lens_by_step, standout, hd=16, vd=24, nh=4, nkv
     return [torch.cat(x) for x in got], want, seqs
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+KERNELS = [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)]
+KERNEL_IDS = ["float32", "bfloat16", "bfloat16-tiled"]
+
+
+@pytest.mark.parametrize("dtype,wide", KERNELS, ids=KERNEL_IDS)
 @pytest.mark.parametrize("edge", ["inside", "outside"])
 @pytest.mark.parametrize("how", ["prompt", "portions", "decoded"])
-def test_attention_window_edge(dtype, edge, how):
+def test_attention_window_edge(dtype, wide, edge, how):
     """The key that stands out sits on the last place the window still holds, or one before it: its value must be
     the output, or must not be in it.  Pages that the window has passed are given back on the way."""
     window, n = 37, 150
     standout = (lambda p: p - window + 1) if edge == "inside" else (lambda p: p - window)
     steps = {"prompt": [[n, 40]], "portions": [[31, 3], [2, 1], [37, 30], [38, 2], [42, 4]],
              "decoded": [[60, 1]] + [[1, 0]] * 90}[how]
-    got, want, seqs = _attention_case(window, 40.0, steps, standout, dtype=dtype)
+    vd = 16 if wide else 24
+    got, want, seqs = _attention_case(window, 40.0, steps, standout, dtype=dtype, vd=vd, wide=wide)
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     for r in range(2):
         n_r = got[r].shape[0]
@@ -323,19 +335,60 @@ def test_attention_window_edge(dtype, edge, how):
     # the oracle itself shows the edge: where the key is seen the output is its value
     v = seqs[0][2].double()
     p = 100
-    close = (want[0][p].view(4, 24)[0] - v[standout(p), 0]).abs().max().item()
+    close = (want[0][p].view(4, vd)[0] - v[standout(p), 0]).abs().max().item()
     assert (close < 1e-2) == (edge == "inside")
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_attention_far_key_among_hundreds_and_first_tokens(dtype):
+@pytest.mark.parametrize("dtype,wide", KERNELS, ids=KERNEL_IDS)
+def test_attention_far_key_among_hundreds_and_first_tokens(dtype, wide):
     """No window: every query's standing-out key is position 1 (far back for late queries, the first tokens for
-    early ones); values wider than keys, capped scores, three requests of unequal length, page borders."""
-    got, want, _ = _attention_case(0, 25.0, [[330, 5, 64], [1, 1, 64], [2, 0, 1], [64, 16, 0]], lambda p: 1, hd=32, vd=8, nh=2,
-                                   nkv=1, dtype=dtype)
+    early ones); values narrower than keys (as wide on the tiled kernel), capped scores, three requests of unequal
+    length, page borders."""
+    got, want, _ = _attention_case(0, 25.0, [[330, 5, 64], [1, 1, 64], [2, 0, 1], [64, 16, 0]], lambda p: 1, hd=32,
+                                   vd=32 if wide else 8, nh=2, nkv=1, dtype=dtype, wide=wide)
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     for r in range(3):
         assert torch.allclose(got[r], want[r], atol=tol, rtol=tol), r
+
+
+def test_tiled_attention_keeps_16_bits_of_queries_and_weights():
+    """Against the same attention with 32-bit queries and weights over the same bfloat16 keys and values: the
+    two-term products leave an error far below one bfloat16 step of the output."""
+    got, want, _ = _attention_case(90, 15.0, [[200, 33], [1, 1], [40, 0]], None, hd=64, vd=64, nh=4, nkv=1, dtype=torch.bfloat16,
+                                   wide=True, norm_eps=1e-6, rot=32)
+    ref, _, _ = _attention_case(90, 15.0, [[200, 33], [1, 1], [40, 0]], None, hd=64, vd=64, nh=4, nkv=1, dtype=torch.bfloat16,
+                                wide=False, norm_eps=1e-6, rot=32)
+    for r in range(2):
+        # both outputs are rounded to bfloat16 (2^-9 relative); they differ by at most one such step, and rarely
+        diff = (got[r] - ref[r]).abs()
+        assert (diff <= 2.0 ** -7 * ref[r].abs() + 1e-3).all(), (diff.max().item(), (diff / (ref[r].abs() + 1e-3)).max().item())
+        assert (diff > 0).double().mean().item() < 0.25
+
+
+@pytest.mark.parametrize("kind", ["relu2", "gelu_tanh", "silu"])
+def test_activation_in_the_products_epilogue(kind):
+    """The decode product (at most 16 rows) and the tensor-memory product of prompt portions apply the feed-forward's
+    activation themselves, into a slice of a wider buffer."""
+    from fastmlx_b200 import kernels as k
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(3)
+    fn = {"relu2": pm.relu_squared, "silu": pm.silu,
+          "gelu_tanh": lambda z: 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))}[kind]
+    x = torch.randn(5, 256, generator=g).bfloat16().to(dev)
+    w = (torch.randn(300, 256, generator=g) * 0.2).bfloat16().to(dev)
+    b = torch.randn(300, generator=g).to(dev)
+    wide = torch.zeros(5, 320, dtype=torch.bfloat16, device=dev)
+    got = k.gemv(x, w, b, act=kind, out=wide[:, 8:308])
+    want = fn((x.double() @ w.double().T + b.double()).bfloat16().double())
+    assert torch.allclose(got.double(), want, rtol=1e-2, atol=1e-2) and wide[:, 308:].abs().max().item() == 0
+    if kind == "relu2":
+        x = torch.randn(256, 512, generator=g).bfloat16().to(dev)
+        w = (torch.randn(1024, 512, generator=g) * 0.1).bfloat16().to(dev)
+        wide = torch.zeros(256, 1024 + 64, dtype=torch.bfloat16, device=dev)
+        got = k.gemm_tcgen05(x, w, epilogue=k.EPI_RELU2, out=wide[:, 64:])
+        want = fn((x.double() @ w.double().T).bfloat16().double())
+        # one bfloat16 step of the product is two of its square
+        assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2) and wide[:, :64].abs().max().item() == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
