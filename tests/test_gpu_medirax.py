@@ -22,6 +22,7 @@ CASES = {
     "M1": dict(lens=[1, 2, 7, 45, 38, 100, 39, 76, 131], page=16, max_tokens=448),
     "M2": dict(lens=[3, 17, 72, 140, 71, 33, 90], page=16, max_tokens=384),
     "M3": dict(lens=[5, 64, 33, 97, 20, 50, 70], page=32, max_tokens=384),
+    "M4": dict(lens=[4, 40, 23, 66, 35, 80], page=16, max_tokens=256),
 }
 
 
@@ -68,7 +69,7 @@ CUTS = {"whole": traces.whole, "tail": traces.tail_decoded, "portions": traces.p
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["M1", "M2", "M3"])
+@pytest.mark.parametrize("name", ["M1", "M2", "M3", "M4"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed", "ones"])
 def test_replay(models, name, dtype, cut):
     d, W, prompts, ref = models[name]
@@ -77,9 +78,8 @@ def test_replay(models, name, dtype, cut):
     outs, rp = _run(d, dtype, steps, case["max_tokens"], case["page"])
     _compare(steps, outs, prompts, ref, TOL[dtype])
     if cut == "mixed":
-        full = [g for g in rp.manager.groups if g.spec.window <= 0 or g.spec.window > 200]
         need = sum(-(-len(t) // case["page"]) for t in prompts.values())
-        assert all(need > g.pool.num_pages for g in full), "the pool is too large for pages to be used again"
+        assert all(need > g.pool.num_pages for g in rp.manager.groups), "the pool is too large for pages to be used again"
         assert len(prompts) > rp.manager.max_requests, "too many slots for one to be used again"
 
 
@@ -437,3 +437,34 @@ def test_greedy_generation_through_the_engine(models, dtype, slack, graphs):
     assert st["pages_used"] == 0
     if graphs:
         assert st["graph_replays"] > 0
+
+
+def test_command_line_and_trace_program(models, tmp_path):
+    """`python -m fastmlx_b200 generate` and bin/trace_run on a Medirax folder, as a user runs them."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    d, W, prompts, ref = models["M4"]
+    out = subprocess.run([sys.executable, "-m", "fastmlx_b200", "generate", "--model-dir", d, "--dtype", "float32", "--prompt-ids",
+                          "5,6,7;9", "--max-tokens", "5", "--temperature", "0", "--max-cache-tokens", "256"], cwd=root,
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [json.loads(x) for x in out.stdout.splitlines() if x.startswith("{")]
+    assert [len(x["output_token_ids"]) for x in lines] == [5, 5]
+    want, margins = _plain_greedy(tm.M4, W, [5, 6, 7], 5)
+    for i, (a, b) in enumerate(zip(lines[0]["output_token_ids"], want)):
+        if a != b:
+            assert margins[i] < 1e-5
+            break
+    sub = {r: prompts[r] for r in ("r1", "r2", "r3")}
+    steps = traces.mixed(sub)
+    outdir = tmp_path / "out"
+    proc = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out", str(outdir),
+                           "--max-tokens", "256"], input="".join(json.dumps(s) + "\n" for s in steps), cwd=root,
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [x for x in proc.stdout.splitlines() if x.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    outs = [np.fromfile(outdir / f"{s['step']}.f32", dtype="<f4").reshape(-1, tm.M4["vocab"]) for s in steps]
+    _compare(steps, outs, sub, ref, TOL["float32"])

@@ -50,4 +50,14 @@ M3 = {
     ],
     "loop": {"start": 0, "stop": 3, "times": 1},
 }
-CONFIGS = {"M1": M1, "M2": M2, "M3": M3}
+# sizes that are multiples of nothing: rows of 25 and 50 bytes, 20-wide heads with 12-wide values
+M4 = {
+    "architecture": "Medirax", "vocab": 101, "width": 50, "logit_scale": 0.8, "norm": {"eps": 1e-5},
+    "layers": [
+        layer("attention", attention(3, 3, 20, 12, 0.22, softcap=9.0, window=33, rot=(6, 777.0)), ff=45),
+        layer("delta", delta(3, 1, 20, 12, 3), ff=45),
+        layer("attention", attention(2, 1, 48, 48, 0.15, softcap=18.0, window=21, rot=(16, 10000.0))),
+    ],
+    "loop": {"start": 0, "stop": 2, "times": 2},
+}
+CONFIGS = {"M1": M1, "M2": M2, "M3": M3, "M4": M4}
