@@ -266,8 +266,11 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], f
     for (int e = 0; e < 4; ++e) {
       const int x = e >> 1;
       const int key = key0 + 8 * j + 2 * t + (e & 1);
-      const float raw = CAP ? cap_l2 * tanhf(s[j][e] * scale_cap) : s[j][e] * sl2;
-      const float v = (!MASK || (key <= lim[x] && key >= lo[x])) ? raw : -INFINITY;
+      float v = -INFINITY;
+      if (!MASK || (key <= lim[x] && key >= lo[x])) {          // the cap is worked out for visible scores only
+        if (CAP) v = cap_l2 * tanhf(s[j][e] * scale_cap);
+        else v = s[j][e] * sl2;
+      }
       s[j][e] = v;
       mx[x] = fmaxf(mx[x], v);
     }
@@ -490,22 +493,22 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
                     const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ row_start,
                     const int* __restrict__ row_ctx, bf16* __restrict__ out, int nh, int nkv, int page_size,
                     long long num_pages, float scale, int window, int* status, float softcap, long long out_stride,
-                    const int* __restrict__ positions) {
+                    const int* __restrict__ positions, float* split_out, int n_splits) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   // The last query tiles of a row see the most keys.  Blocks start in the order x, y, z: with the
   // tile index in z the longest blocks of every head and row start first.
-  const int r = blockIdx.y, g = blockIdx.x, tile = gridDim.z - 1 - blockIdx.z;
+  // n_splits > 1 (rows of one token each): the grid's z counts shares of a row's keys instead of query tiles
+  const bool shared_keys = WIDE && n_splits > 1;
+  const int r = blockIdx.y, g = blockIdx.x, tile = shared_keys ? 0 : gridDim.z - 1 - blockIdx.z;
+  const int split = shared_keys ? blockIdx.z : 0;
   const int rep = nh / nkv;
   const int t0 = row_start[r], q_len = row_start[r + 1] - t0, ctx = row_ctx[r];
   const int n_packed = q_len * rep;
   const int prow0 = tile * BM;
   if (prow0 >= n_packed || ctx < 0) return;
-  if (WIDE && positions != nullptr && positions[t0] < 0) {
-    // a padding row of a captured step (one token at position -1): it sees no key and its output is zero
-    for (int i = threadIdx.x; i < rep * HD; i += THREADS) out[(long long)t0 * out_stride + (long long)g * rep * HD + i] = __float2bfloat16_rn(0.f);
-    return;
-  }
+  // a padding row of a captured step (one token at position -1) sees no key: its output is zero
+  const bool padding = WIDE && positions != nullptr && positions[t0] < 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
   const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages,
                 page_shift_of(page_size)};
@@ -553,7 +556,11 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   const int kbeg = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
   const int kend = ctx + last_tok + 1;
   const int kstart = kbeg & ~3;                       // tiles start on a multiple of 4 keys
-  const int n_tiles = (kend - kstart + BN - 1) / BN;
+  const int all_tiles = padding ? 0 : (kend - kstart + BN - 1) / BN;
+  // this block's tiles: all of them, or its share of the row's
+  const int per_split = shared_keys ? (all_tiles + n_splits - 1) / n_splits : all_tiles;
+  const int tile0 = split * per_split;
+  const int n_tiles = max(0, min(all_tiles, tile0 + per_split) - tile0);
   const float sl2 = scale * LOG2E;
   // what every row of this warp sees for sure: keys from the last row's window start up to
   // the first row's position; tiles inside that span need no mask
@@ -573,7 +580,7 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   auto stage_v = [&](int s) { return smem + (size_t)s * 2 * TILE + TILE; };
 #pragma unroll
   for (int s = 0; s < PREFILL_STAGES - 1; ++s) {
-    if (s < n_tiles) load_tiles(stage_k(s), stage_v(s), c, g, kstart + s * BN, kbeg, kend, status, r);
+    if (s < n_tiles) load_tiles(stage_k(s), stage_v(s), c, g, kstart + (tile0 + s) * BN, kbeg, kend, status, r);
     cp_async_commit();
   }
   for (int it = 0; it < n_tiles; ++it) {
@@ -581,10 +588,11 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
     __syncthreads();
     const int nx = it + PREFILL_STAGES - 1;
     if (nx < n_tiles)
-      load_tiles(stage_k(nx % PREFILL_STAGES), stage_v(nx % PREFILL_STAGES), c, g, kstart + nx * BN, kbeg, kend, status, r);
+      load_tiles(stage_k(nx % PREFILL_STAGES), stage_v(nx % PREFILL_STAGES), c, g, kstart + (tile0 + nx) * BN, kbeg, kend, status, r);
     cp_async_commit();
     const bf16* ks = stage_k(it % PREFILL_STAGES);
     const bf16* vs = stage_v(it % PREFILL_STAGES);
+    if (WIDE && prow0 + warp * 16 >= n_packed) continue;        // a warp without a row (the rows of one token fill one warp at most) only copies
     float s[BN / 8][4];
 #pragma unroll
     for (int j = 0; j < BN / 8; ++j)
@@ -592,7 +600,7 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
       for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
     qk_tile<BN / 8, WIDE>(s, qf, ks, 0, qf2);
     float alpha[2];
-    const int tk0 = kstart + it * BN;
+    const int tk0 = kstart + (tile0 + it) * BN;
     const bool open = warp_full && tk0 >= sure_lo && tk0 + BN - 1 <= sure_hi;
     if (capped && open)
       softmax_step<BN / 8, false, true>(s, m, l, alpha, sl2, tk0, lim, lo, cap_l2, scale_cap);
@@ -615,11 +623,56 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
     l[x] += __shfl_xor_sync(0xffffffffu, l[x], 1);
     l[x] += __shfl_xor_sync(0xffffffffu, l[x], 2);
     if (!rvalid[x]) continue;
+    if (shared_keys) {
+      // this share's output as it stands (not yet divided), with its maximum (scaled, base 2) and its sum
+      float* part = split_out + (((long long)(t0 + tok[x]) * nh + head[x]) * n_splits + split) * (HD + 2);
+#pragma unroll
+      for (int n = 0; n < NT_O; ++n) *reinterpret_cast<float2*>(part + 8 * n + 2 * tq) = make_float2(o[n][2 * x], o[n][2 * x + 1]);
+      if (tq == 0) *reinterpret_cast<float2*>(part + HD) = make_float2(m[x], l[x]);
+      continue;
+    }
     const float inv = l[x] > 0.f ? 1.0f / l[x] : 0.f;
     bf16* op = out + (long long)(t0 + tok[x]) * out_stride + (long long)head[x] * HD + 2 * tq;
 #pragma unroll
     for (int n = 0; n < NT_O; ++n)
       *reinterpret_cast<unsigned*>(op + 8 * n) = pack_bf16(o[n][2 * x] * inv, o[n][2 * x + 1] * inv);
+  }
+}
+
+// The shares of a row's keys put together, one warp per (token, head), in share order: out = sum_s o_s 2^(m_s - M) /
+// sum_s l_s 2^(m_s - M) with M the largest of the shares' maxima; a row that saw no key gets zeros.
+__global__ void __launch_bounds__(128)
+attn_wide_combine_kernel(const float* part, bf16* out, long long out_stride, long long n_items, int nh, int n_splits) {
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= n_items) return;
+  const long long t = item / nh;
+  const int h = (int)(item - t * nh);
+  const float* p = part + item * n_splits * (HD + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[s * (HD + 2) + HD]);
+  float L = 0.f;
+  float acc[(HD + 31) / 32];
+#pragma unroll
+  for (int i = 0; i < (HD + 31) / 32; ++i) acc[i] = 0.f;
+  if (M != -INFINITY) {
+    for (int s = 0; s < n_splits; ++s) {
+      const float* ps = p + s * (HD + 2);
+      const float w = fast_exp2(ps[HD] - M);
+      L += ps[HD + 1] * w;
+#pragma unroll
+      for (int i = 0; i < (HD + 31) / 32; ++i) {
+        const int e = lane + 32 * i;
+        if (e < HD) acc[i] = fmaf(ps[e], w, acc[i]);
+      }
+    }
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  bf16* op = out + t * out_stride + (long long)h * HD;
+#pragma unroll
+  for (int i = 0; i < (HD + 31) / 32; ++i) {
+    const int e = lane + 32 * i;
+    if (e < HD) op[e] = __float2bfloat16_rn(acc[i] * inv);
   }
 }
 
@@ -1135,7 +1188,7 @@ FMX_EXPORT int fmx_attn_prefill(const void* q, long long q_stride, const void* k
   dim3 grid(nkv, rows, (unsigned)tiles);
   attn_prefill_kernel<false><<<grid, THREADS, prefill_smem(), stream>>>(
       q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv,
-      page_size, num_pages, scale, window, status, 0.f, (long long)nh * HD, (const int*)nullptr);
+      page_size, num_pages, scale, window, status, 0.f, (long long)nh * HD, (const int*)nullptr, (float*)nullptr, 1);
   FMX_LAUNCH_CHECK();
   return 0;
 }
@@ -1147,6 +1200,7 @@ FMX_EXPORT int fmx_attn_prefill_wide(const float* q, long long q_stride, const v
                                      int bt_stride, const int* row_start, const int* row_ctx, const int* positions, void* out,
                                      long long out_stride, int rows, int max_q_len, int nh, int nkv, int page_size,
                                      long long num_pages, float scale, float softcap, int window, int* status,
+                                     float* scratch, long long scratch_floats, int n_splits, int n_tokens,
                                      cudaStream_t stream) {
   if (rows == 0 || max_q_len == 0) return 0;
   if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0)
@@ -1165,10 +1219,35 @@ FMX_EXPORT int fmx_attn_prefill_wide(const float* q, long long q_stride, const v
   const int rep = nh / nkv;
   const long long tiles = ((long long)max_q_len * rep + BM - 1) / BM;
   if (tiles > 65535) return fmx_fail("fmx_attn_prefill_wide: %d query tokens in one row are too many for one launch", max_q_len);
+  if (n_splits > 1) {
+    // rows of one token each (their tokens are [first token of the first row, + rows)): the keys of a row are shared
+    // out over n_splits blocks, which leave their parts in `scratch` for the combining kernel
+    if (max_q_len != 1) return fmx_fail("fmx_attn_prefill_wide: only rows of one token share their keys out over blocks");
+    if (scratch == nullptr || (long long)n_tokens * nh * n_splits * (HD + 2) > scratch_floats)
+      return fmx_fail("fmx_attn_prefill_wide: the workspace is too small for %d shares of %d tokens", n_splits, n_tokens);
+    dim3 grid(nkv, rows, (unsigned)n_splits);
+    attn_prefill_kernel<true><<<grid, THREADS, prefill_smem(), stream>>>(
+        q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size,
+        num_pages, scale, window, status, softcap, out_stride, positions, scratch, n_splits);
+    FMX_LAUNCH_CHECK();
+    return 0;
+  }
   dim3 grid(nkv, rows, (unsigned)tiles);
   attn_prefill_kernel<true><<<grid, THREADS, prefill_smem(), stream>>>(
       q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size,
-      num_pages, scale, window, status, softcap, out_stride, positions);
+      num_pages, scale, window, status, softcap, out_stride, positions, (float*)nullptr, 1);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
+// Second half of a launch with n_splits > 1: tokens [first_token, first_token + n_tokens) of the step.
+FMX_EXPORT int fmx_attn_wide_combine(const float* scratch, void* out, long long out_stride, int first_token, int n_tokens,
+                                     int nh, int n_splits, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  const long long items = (long long)n_tokens * nh;
+  attn_wide_combine_kernel<<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(
+      scratch + (long long)first_token * nh * n_splits * (HD + 2), (bf16*)out + (long long)first_token * out_stride, out_stride,
+      items, nh, n_splits);
   FMX_LAUNCH_CHECK();
   return 0;
 }

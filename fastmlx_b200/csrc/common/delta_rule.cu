@@ -146,10 +146,21 @@ delta_rule_kernel(const float* qkv, const float* gb, const int* row_start, const
   const int colc = live ? col : Dv - 1;          // lanes beyond the last column follow it and write nothing
   float* sp = state + (long long)slot * slot_stride + ((long long)h * Dv + colc) * D;
   float S[NPL], k[NPL], q[NPL];
+  // a lane's share of a column in 16-byte accesses where the slots allow it
+  const bool vec = (D & 3) == 0 && (slot_stride & 3) == 0 && (((uintptr_t)state) & 15) == 0;
+  if (vec) {
 #pragma unroll
-  for (int i = 0; i < NPL; ++i) {
-    const int d = sub * NPL + i;
-    S[i] = d < D ? sp[d] : 0.f;
+    for (int i = 0; i < NPL; i += 4) {
+      const int d = sub * NPL + i;
+      const float4 x = d < D ? *reinterpret_cast<const float4*>(sp + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+      S[i] = x.x; S[i + 1] = x.y; S[i + 2] = x.z; S[i + 3] = x.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int d = sub * NPL + i;
+      S[i] = d < D ? sp[d] : 0.f;
+    }
   }
   const long long qoff = (long long)g * D, koff = (long long)(G + g) * D, voff = (long long)2 * G * D + (long long)h * Dv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -229,7 +240,13 @@ delta_rule_kernel(const float* qkv, const float* gb, const int* row_start, const
     }
     __syncthreads();                             // the run is walked: its buffer may take the run after the next
   }
-  if (live) {
+  if (live && vec) {
+#pragma unroll
+    for (int i = 0; i < NPL; i += 4) {
+      const int d = sub * NPL + i;
+      if (d < D) *reinterpret_cast<float4*>(sp + d) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+    }
+  } else if (live) {
 #pragma unroll
     for (int i = 0; i < NPL; ++i) {
       const int d = sub * NPL + i;

@@ -214,9 +214,9 @@ class NativeProgram:
         if len(manager.groups) > MAX_GROUPS:
             raise NotNative(f"the native executor takes up to {MAX_GROUPS} cache groups")
         self.model, self.manager, self.rt, self.status = model, manager, rt, status
-        self.lib = host_library()
         b = ProgramBuilder(rt, manager)
         model.emit(b)                                  # raises NotNative where a part cannot describe itself
+        self.lib = host_library()                      # built and loaded only for a model that runs through it
         self.builder = b
         k = rt.k
         table = FmxKernelTable()

@@ -367,19 +367,63 @@ def wide_attention_ok(q, kv, hd, vd) -> bool:
             and hd % 16 == 0 and hd <= 256 and q.stride(0) % 2 == 0 and q.data_ptr() % 8 == 0)
 
 
+WIDE_MAX_SPLITS = 16
+
+
+def wide_attention_splits(rows: int, nkv: int, keys: int, device=None) -> int:
+    """Blocks that share the keys of a one-token row out among them: enough for about two blocks per SM, each with
+    at least two 64-key tiles.  `keys`: the most keys a row sees (its window, or the longest context)."""
+    tiles = -(-max(1, int(keys)) // 64) + 1
+    want = -(-2 * num_sms(device) // max(1, rows * nkv))
+    return max(1, min(want, tiles // 2, WIDE_MAX_SPLITS))
+
+
+def _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, first_token: int = 0, splits: int = 1) -> None:
+    bt = group.block_tables
+    scratch = None
+    n_tokens = ctx.R
+    if splits > 1:
+        scratch = attention_scratch(q.device, (first_token + n_tokens) * nh * splits * (hd + 2))
+    call(f"attn_hd{hd}", "fmx_attn_prefill_wide", q.data_ptr(), q.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
+         ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), out.stride(0), ctx.R,
+         int(ctx.max_q_len), nh, nkv, kv.shape[3], kv.shape[0], float(scale), float(softcap or 0.0), int(window),
+         _ptr(ctx.status), _ptr(scratch), scratch.numel() if scratch is not None else 0, int(splits),
+         first_token + n_tokens, _stream())
+    if splits > 1:
+        call(f"attn_hd{hd}", "fmx_attn_wide_combine", scratch.data_ptr(), out.data_ptr(), out.stride(0), int(first_token),
+             n_tokens, nh, int(splits), _stream())
+
+
 def paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out=None) -> torch.Tensor:
     """Attention of any mix of rows on the tensor cores with 32-bit scores and weights: the 32-bit queries
     q[T, nh*hd] and the probabilities enter the products as two bfloat16 terms each, sums are 32-bit, scores may be
-    capped (softcap > 0).  `out` may be a slice of a wider buffer.  -> [T, nh*hd] in bfloat16."""
+    capped (softcap > 0).  `out` may be a slice of a wider buffer.  -> [T, nh*hd] in bfloat16.  The one-token rows
+    (a whole decode step, or the rows at the head of a mixed step) have their keys shared out over several blocks
+    whose parts a second kernel puts together; the portions behind them take a launch of their own."""
     T = q.shape[0]
     if out is None:
         out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=q.device)
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
-    bt = group.block_tables
-    call(f"attn_hd{hd}", "fmx_attn_prefill_wide", q.data_ptr(), q.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
-         ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), out.stride(0), ctx.R,
-         int(ctx.max_q_len), nh, nkv, kv.shape[3], kv.shape[0], float(scale), float(softcap or 0.0), int(window),
-         _ptr(ctx.status), _stream())
+    d = ctx.R if ctx.all_decode else getattr(ctx, "decode_rows", 0)
+    if d <= 0:
+        _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out)
+        return out
+    longest = ctx.max_ctx_after if ctx.all_decode else ctx.decode_max_ctx
+    keys = min(window, longest) if window > 0 else longest
+    splits = wide_attention_splits(d, nkv, keys, q.device)
+    if splits > 1 and d * nh * splits * (hd + 2) > ATTN_SCRATCH_FLOATS:
+        splits = 1
+    if ctx.all_decode:
+        _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, 0, splits)
+        return out
+    key = ("wide attention rows", id(group))
+    views = ctx.scratch.get(key)
+    if views is None:
+        views = ctx.scratch[key] = (_rows_of(ctx, group, 0, d, 1, ctx.decode_max_ctx),
+                                    _rows_of(ctx, group, d, ctx.R, ctx.rest_max_q_len, ctx.rest_max_ctx))
+    (dctx, dgroup), (rctx, rgroup) = views
+    _wide_launch(q, kv, dctx, dgroup, nh, nkv, hd, scale, softcap, window, out, 0, splits)     # the one-token rows come first
+    _wide_launch(q, kv, rctx, rgroup, nh, nkv, hd, scale, softcap, window, out)
     return out
 
 

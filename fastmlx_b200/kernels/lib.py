@@ -51,7 +51,9 @@ _SIGNATURES = {
     "attn": {
         "fmx_attn_prefill_tc": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _I, _P, _L, _P],
         "fmx_attn_prefill": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],
-        "fmx_attn_prefill_wide": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _L, _F, _F, _I, _P, _P],
+        "fmx_attn_prefill_wide": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _L, _F, _F, _I, _P, _P, _L, _I, _I,
+                                  _P],
+        "fmx_attn_wide_combine": [_P, _P, _L, _I, _I, _I, _I, _P],
         "fmx_attn_decode": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P, _I, _I, _I, _P],
     },
 }

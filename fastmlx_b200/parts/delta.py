@@ -66,7 +66,9 @@ class GatedDeltaMixer(Mixer):
         self.a_log, self.dt_bias, self.norm_w = (to_f32_vector(tensors[n], rt) for n in self.vec_names)
 
     def state_spec(self):
-        return StateSpec((self.s_floats + (self.taps - 1) * self.channels,), torch.float32)
+        # a multiple of four floats, so that every slot starts on 16 bytes
+        n = self.s_floats + (self.taps - 1) * self.channels
+        return StateSpec((-(-n // 4) * 4,), torch.float32)
 
     def forward_inner(self, x, ctx, cache, out=None):
         """The normalised, gated read-outs of all heads side by side, [T, heads * vdim]."""

@@ -365,6 +365,20 @@ def test_tiled_attention_keeps_16_bits_of_queries_and_weights():
         assert (diff > 0).double().mean().item() < 0.25
 
 
+def test_tiled_attention_shares_a_rows_keys_out_over_blocks():
+    """Steps of single tokens behind long contexts (and such rows at the head of a mixed step): several blocks take
+    shares of a row's keys and a second kernel puts their parts together."""
+    from fastmlx_b200 import kernels as k
+    assert k.wide_attention_splits(3, 2, 701) > 1
+    steps = [[700, 300, 5]] + [[1, 1, 1]] * 6 + [[1, 1, 40]] * 2 + [[1, 0, 1]]
+    got, want, _ = _attention_case(0, 20.0, steps, lambda p: 3, hd=32, vd=32, nh=4, nkv=2, dtype=torch.bfloat16, wide=True)
+    for r in range(3):
+        assert torch.allclose(got[r], want[r], atol=2e-2, rtol=2e-2), r
+    got, want, _ = _attention_case(300, 0.0, [[650, 420]] + [[1, 1]] * 5, None, hd=64, vd=64, nh=8, nkv=1, dtype=torch.bfloat16, wide=True)
+    for r in range(2):
+        assert torch.allclose(got[r], want[r], atol=2e-2, rtol=2e-2), r
+
+
 @pytest.mark.parametrize("kind", ["relu2", "gelu_tanh", "silu"])
 def test_activation_in_the_products_epilogue(kind):
     """The decode product (at most 16 rows) and the tensor-memory product of prompt portions apply the feed-forward's

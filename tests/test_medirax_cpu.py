@@ -72,6 +72,7 @@ def test_cache_manager_lays_out_values_of_another_width():
     m = CacheManager(model.cache_needs(), page_size=8, num_pages=6, max_requests=2, dtype=torch.float32)
     assert m.entries[0].kv.shape == (6, 2 * 8 * (24 + 40)) and m.entries[5].kv.shape == (6, 2, 1, 8, 32)
     assert m.entries[1].state.shape == (2, 4 * 40 * 24 + 2 * (2 * 2 * 24 + 4 * 40)) and m.entries[0].state is None
+    assert m.entries[2].state.shape == (2, 2 * 16 * 16 + 1 * (2 * 2 * 16 + 2 * 16))
     assert m.bytes_per_token() == 4 * (2 * (24 + 40) + 2 * 32)
 
 
