@@ -510,6 +510,11 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   // a padding row of a captured step (one token at position -1) sees no key: its output is zero
   const bool padding = WIDE && positions != nullptr && positions[t0] < 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+  // A row of one token has at most 16 packed rows (its heads): they fit one warp's MMA rows.  Then all four warps take
+  // those rows and a quarter of every key tile each (16 keys), and their parts are added up at the end, instead of
+  // three warps standing by while the first walks every key.
+  const bool one_token = WIDE && q_len == 1 && rep <= 16;
+  const int wrow = one_token ? 0 : warp * 16;      // the first packed row of this warp within the block's tile
   const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages,
                 page_shift_of(page_size)};
 
@@ -518,7 +523,7 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   bool rvalid[2];
 #pragma unroll
   for (int x = 0; x < 2; ++x) {
-    prow[x] = prow0 + warp * 16 + gq + 8 * x;
+    prow[x] = prow0 + wrow + gq + 8 * x;
     rvalid[x] = prow[x] < n_packed;
     const int pr = rvalid[x] ? prow[x] : n_packed - 1;
     tok[x] = pr / rep;
@@ -564,8 +569,8 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   const float sl2 = scale * LOG2E;
   // what every row of this warp sees for sure: keys from the last row's window start up to
   // the first row's position; tiles inside that span need no mask
-  const int wfirst = min(prow0 + warp * 16, n_packed - 1) / rep, wlast = min(prow0 + warp * 16 + 15, n_packed - 1) / rep;
-  const bool warp_full = prow0 + warp * 16 + 15 < n_packed;
+  const int wfirst = min(prow0 + wrow, n_packed - 1) / rep, wlast = min(prow0 + wrow + 15, n_packed - 1) / rep;
+  const bool warp_full = prow0 + wrow + 15 < n_packed;
   const int sure_lo = window > 0 ? max(0, ctx + wlast - window + 1) : 0;
   const int sure_hi = ctx + wfirst;
 
@@ -592,7 +597,27 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
     cp_async_commit();
     const bf16* ks = stage_k(it % PREFILL_STAGES);
     const bf16* vs = stage_v(it % PREFILL_STAGES);
-    if (WIDE && prow0 + warp * 16 >= n_packed) continue;        // a warp without a row (the rows of one token fill one warp at most) only copies
+    if (WIDE && prow0 + wrow >= n_packed) continue;             // a warp without a row only copies
+    if (one_token) {
+      // this warp's quarter of the tile: 16 keys against the row's heads
+      float s2[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s2[j][e] = 0.f;
+      qk_tile<2, WIDE>(s2, qf, ks, 16 * warp, qf2);
+      float alpha[2];
+      const int qk0 = kstart + (tile0 + it) * BN + 16 * warp;
+      if (capped) softmax_step<2, true, true>(s2, m, l, alpha, sl2, qk0, lim, lo, cap_l2, scale_cap);
+      else softmax_step<2, true>(s2, m, l, alpha, sl2, qk0, lim, lo);
+#pragma unroll
+      for (int n = 0; n < NT_O; ++n) {
+        o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+        o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+      }
+      pv_tile<1, WIDE>(o, s2, vs, 16 * warp);
+      continue;
+    }
     float s[BN / 8][4];
 #pragma unroll
     for (int j = 0; j < BN / 8; ++j)
@@ -618,6 +643,46 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
     pv_tile<BN / 16, WIDE>(o, s, vs, 0);
   }
   cp_async_wait<0>();
+  if (one_token) {
+    // the four warps' parts of the same rows, added up in warp order through the tiles' shared memory
+    __syncthreads();
+    float* red = reinterpret_cast<float*>(smem_raw);           // [4][16][HD + 2]
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      l[x] += __shfl_xor_sync(0xffffffffu, l[x], 1);
+      l[x] += __shfl_xor_sync(0xffffffffu, l[x], 2);
+      float* mine = red + (warp * 16 + gq + 8 * x) * (HD + 2);
+#pragma unroll
+      for (int n = 0; n < NT_O; ++n) *reinterpret_cast<float2*>(mine + 8 * n + 2 * tq) = make_float2(o[n][2 * x], o[n][2 * x + 1]);
+      if (tq == 0) *reinterpret_cast<float2*>(mine + HD) = make_float2(m[x], l[x]);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rep * HD; idx += THREADS) {
+      const int row = idx / HD, e = idx - row * HD;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, red[(w * 16 + row) * (HD + 2) + HD]);
+      float L = 0.f, O = 0.f;
+      if (M != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float* pw = red + (w * 16 + row) * (HD + 2);
+          const float f = fast_exp2(pw[HD] - M);
+          L = fmaf(pw[HD + 1], f, L);
+          O = fmaf(pw[e], f, O);
+        }
+      }
+      const int hq = g * rep + row;
+      if (shared_keys) {
+        float* part = split_out + (((long long)t0 * nh + hq) * n_splits + split) * (HD + 2);
+        part[e] = O;
+        if (e == 0) { part[HD] = M; part[HD + 1] = L; }
+      } else {
+        out[(long long)t0 * out_stride + (long long)hq * HD + e] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int x = 0; x < 2; ++x) {
     l[x] += __shfl_xor_sync(0xffffffffu, l[x], 1);
