@@ -13,7 +13,7 @@
 //                     (q also times D^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)).
 //   conv_state_update per request: the last taps-1 inputs of the portion replace the convolution state.
 //   delta_rule        the recurrence.  Columns of S are independent (column j needs v_j only), so a column is
-//                     given to 2 to 8 adjacent lanes that hold 16 (or 32) of its values each in registers; the
+//                     given to 8 to 32 adjacent lanes that hold 8 of its values each in registers; the
 //                     tokens of a request's portion are walked in order, their operands staged through shared
 //                     memory a run of tokens ahead.
 //   gated_rmsnorm     o of each head divided by its root mean square, times a weight, times SiLU(gate).
@@ -321,13 +321,19 @@ FMX_EXPORT int fmx_delta_rule(const float* qkv, const float* gb, const int* row_
   do {                                                                                                                 \
     constexpr int cols = 128 / (L), rowf = (2 * (NPL) * (L) + cols + 2 + 3) / 4 * 4;                                   \
     const dim3 grid((Dv + cols - 1) / cols, H, R);                                                                     \
-    fmx_launch(delta_rule_kernel<NPL, L, TB>, grid, dim3(128), (size_t)2 * (TB) * rowf * sizeof(float), stream, qkv, gb, \
-               row_start, row_slot, state, slot_stride, out, H, G, D, Dv, max_slots);                                  \
+    constexpr size_t smem = (size_t)2 * (TB) * rowf * sizeof(float);                                                   \
+    if (smem > 48 * 1024)                                                                                              \
+      cudaFuncSetAttribute(delta_rule_kernel<NPL, L, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    fmx_launch(delta_rule_kernel<NPL, L, TB>, grid, dim3(128), smem, stream, qkv, gb, row_start, row_slot, state,      \
+               slot_stride, out, H, G, D, Dv, max_slots);                                                              \
   } while (0)
   // Lanes per column: few lanes make a step's sums over lanes short, many lanes make its dots short and give the
   // grid more warps.  `lanes` = 0 leaves the choice here.
-  if (lanes == 0) lanes = 8;
-  if (lanes != 2 && lanes != 4 && lanes != 8) return fmx_fail("fmx_delta_rule: 2, 4 or 8 lanes per column, not %d", lanes);
+  // Measured (us for 2,048 tokens of one request, 32 heads): dim 64: 8 lanes 524, 16 lanes 549, 4 lanes 600; dim 128: 8 lanes
+  // 1,345, 16 lanes 963: eight rows of state per lane.
+  if (lanes == 0) lanes = D <= 64 ? 8 : D <= 128 ? 16 : 32;
+  if (lanes != 2 && lanes != 4 && lanes != 8 && lanes != 16 && lanes != 32)
+    return fmx_fail("fmx_delta_rule: 2, 4, 8, 16 or 32 lanes per column, not %d", lanes);
   const int per_lane = (D + lanes - 1) / lanes;
   if (per_lane > 32) return fmx_fail("fmx_delta_rule: %d rows of state are too many for %d lanes per column", D, lanes);
 #define FMX_DELTA_LANES(L)                      \
@@ -339,7 +345,9 @@ FMX_EXPORT int fmx_delta_rule(const float* qkv, const float* gb, const int* row_
   } while (0)
   if (lanes == 2) FMX_DELTA_LANES(2);
   else if (lanes == 4) FMX_DELTA_LANES(4);
-  else FMX_DELTA_LANES(8);
+  else if (lanes == 8) FMX_DELTA_LANES(8);
+  else if (lanes == 16) FMX_DELTA_LANES(16);
+  else FMX_DELTA_LANES(32);
 #undef FMX_DELTA_LANES
 #undef FMX_DELTA_RULE
   FMX_LAUNCH_CHECK();

@@ -452,7 +452,7 @@ def delta_prepare(proj, ab, conv_w, a_log, dt_bias, ctx, state, conv_off, H, G, 
 def delta_rule(qkv, gb, ctx, state, H, G, D, Dv, lanes: int = 0) -> torch.Tensor:
     """The gated delta rule over every request's tokens of the step, in order, from and into the requests'
     state slots (S^T per head, [H, Dv, D], at the head of a slot): S <- g S; u = beta (v - S^T k);
-    S <- S + k u^T; o = S^T q.  `lanes` (2, 4, 8; 0: the library's choice): lanes that share a column of S.
+    S <- S + k u^T; o = S^T q.  `lanes` (2 to 32, a power of two; 0: the library's choice): lanes that share a column of S.
     -> o in 32-bit, [T, H*Dv]."""
     T = qkv.shape[0]
     out = torch.empty((T, H * Dv), dtype=torch.float32, device=qkv.device)
