@@ -482,3 +482,21 @@ def test_command_line_and_trace_program(models, tmp_path):
     assert [x for x in proc.stdout.splitlines() if x.startswith("done ")] == [f"done {s['step']}" for s in steps]
     outs = [np.fromfile(outdir / f"{s['step']}.f32", dtype="<f4").reshape(-1, tm.M4["vocab"]) for s in steps]
     _compare(steps, outs, sub, ref, TOL["float32"])
+
+
+def test_preemption_recomputes_state_and_changes_no_token(models):
+    """A pool too small for three requests to grow together: the scheduler preempts the newest, frees its pages and its
+    state slot, and recomputes it later from zero state; in 32-bit every request still produces what it produces with
+    room to spare."""
+    from fastmlx_b200 import Engine, SamplingParams
+    d, W, _, _ = models["M2"]                        # one of its attention layers keeps every key
+    prompts = [tiny.rand_tokens(n, tm.M2["vocab"], 900 + n) for n in (30, 28, 25)]
+    sp = SamplingParams(max_tokens=40, temperature=0.0)
+    tight = Engine(d, dtype="float32", block_size=8, initial_cache_blocks=18, max_concurrent_requests=4)
+    outs = tight.generate(prompts, sp)
+    assert tight.stats()["preemptions"] > 0
+    roomy = Engine(d, dtype="float32", block_size=8, initial_cache_blocks=64, max_concurrent_requests=4)
+    assert [o.output_token_ids for o in outs] == [o.output_token_ids for o in roomy.generate(prompts, sp)]
+    assert all(o.finish_reason == "length" and len(o.output_token_ids) == 40 for o in outs)
+    assert tight.stats()["pages_used"] == 0
+    tight.manager.check()
