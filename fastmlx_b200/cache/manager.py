@@ -31,8 +31,7 @@ class CacheGroup:
     kv: torch.Tensor | None = None      # [len(entries), num_pages, 2, nkv, page_size, hd]
 
     def page_bytes(self, elem: int) -> int:
-        return self.spec.num_kv_heads * self.pool.page_size * (self.spec.head_dim + self.spec.value_dim) * elem \
-            * len(self.entries)
+        return self.spec.num_kv_heads * self.pool.page_size * self.spec.token_width * elem * len(self.entries)
 
 
 @dataclass
@@ -81,7 +80,9 @@ class CacheManager:
             self.groups[g].entries.append(pos)
         if allocate:
             for g in self.groups:
-                if g.spec.value_dim == g.spec.head_dim:
+                if g.spec.values_are_keys:      # keys only
+                    shape = (1, g.spec.num_kv_heads, page_size, g.spec.head_dim)
+                elif g.spec.value_dim == g.spec.head_dim:
                     shape = (2, g.spec.num_kv_heads, page_size, g.spec.head_dim)
                 else:           # keys, then values of another width: a page is one run of elements
                     shape = (g.spec.num_kv_heads * page_size * (g.spec.head_dim + g.spec.value_dim),)
@@ -117,8 +118,8 @@ class CacheManager:
         e = torch.empty((), dtype=self.dtype).element_size()
         total = 0
         for g in self.groups:
-            n = req.length if g.spec.window <= 0 else min(req.length, g.spec.window)
-            total += g.spec.num_kv_heads * (g.spec.head_dim + g.spec.value_dim) * e * len(g.entries) * n
+            n = req.length if g.spec.window <= 0 else min(req.length, g.spec.window + g.spec.keep_first)
+            total += g.spec.num_kv_heads * g.spec.token_width * e * len(g.entries) * n
         return total
 
     @property
@@ -142,7 +143,8 @@ class CacheManager:
         for g in self.groups:
             room = g.pool.num_pages * self.page_size
             w = g.spec.window
-            need = n_tokens if w <= 0 else min(n_tokens, w + min(portion, n_tokens) + self.page_size)
+            kept = -(-g.spec.keep_first // self.page_size) * self.page_size
+            need = n_tokens if w <= 0 else min(n_tokens, w + min(portion, n_tokens) + self.page_size + kept)
             if need > room:
                 return room
         return 0
@@ -221,8 +223,11 @@ class CacheManager:
             w = g.spec.window
             if w <= 0:
                 continue
-            # the next query sits at position >= length and sees keys > position - w
+            # the next query sits at position >= length and sees keys > position - w; the pages of the
+            # first tokens that every query keeps seeing stay
             first_needed = req.length - w + 1
+            bt.kept = max(bt.kept, min(-(-g.spec.keep_first // self.page_size), len(bt.pages)))
+            bt.first_live = max(bt.first_live, bt.kept)
             while bt.first_live < len(bt.pages) and (bt.first_live + 1) * self.page_size <= first_needed:
                 g.pool.give([bt.pages[bt.first_live]])
                 bt.pages[bt.first_live] = -1
@@ -234,7 +239,7 @@ class CacheManager:
         req = self.requests.pop(request_id)
         for gi, (g, bt) in enumerate(zip(self.groups, req.tables)):
             g.pool.give(bt.live())
-            bt.pages, bt.first_live = [], 0
+            bt.pages, bt.first_live, bt.kept = [], 0, 0
             self.table_mirror[gi][req.slot, :] = -1
         self._free_slots.append(req.slot)
 
@@ -258,7 +263,7 @@ class CacheManager:
             held = []
             for r in self.requests.values():
                 bt = r.tables[gi]
-                assert all(p == -1 for p in bt.pages[:bt.first_live])
+                assert all(p == -1 for p in bt.pages[bt.kept:bt.first_live]) and all(p >= 0 for p in bt.pages[:bt.kept])
                 held.extend(bt.live())
             assert len(held) == len(set(held)), "a page is in two block tables"
             assert all(0 <= p < g.pool.num_pages for p in held)

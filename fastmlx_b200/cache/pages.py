@@ -50,11 +50,13 @@ class PagePool:
 
 class BlockTable:
     """Pages of one request in one group: entry i holds tokens [i*page_size, (i+1)*page_size).
-    An entry is -1 once a window has passed it and its page was given back."""
+    An entry is -1 once a window has passed it and its page was given back; the first `kept`
+    entries (the pages of tokens that stay visible behind a window) are never given back."""
 
     def __init__(self):
         self.pages: list[int] = []
-        self.first_live = 0          # entries before this one are -1
+        self.first_live = 0          # entries kept .. first_live - 1 are -1
+        self.kept = 0
 
     def live(self) -> list[int]:
-        return self.pages[self.first_live:]
+        return self.pages[:min(self.kept, self.first_live)] + self.pages[self.first_live:]

@@ -14,12 +14,19 @@
 // before the softmax.  A page holds its keys [nkv, page_size, hd] and then its values
 // [nkv, page_size, vd]; with hd = vd that is the layout [2, nkv, page_size, hd] of the other
 // attention kernels.  The output's rows may be wider than nh * vd (a slice of a joined buffer).
+//
+// Three further options.  `keep_first` > 0 beside a window: the first keep_first positions of a
+// request stay visible to every later query (at their true positions); their chunks are walked
+// first, in position order like the rest.  `values_are_keys`: a page holds keys only,
+// [nkv, page_size, hd], and the values are those same vectors (vd = hd): attention over a cached
+// latent.  `gate` (32-bit, [T, nh * vd] in rows of gate_stride): the output is multiplied element by
+// element with sigmoid(gate).
 #include <math.h>
 #include "common.cuh"
 
 namespace {
 constexpr int WARPS = 4;
-constexpr int MAX_HD = 256;
+constexpr int MAX_HD = 512;
 
 template <typename TQ, typename T>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -27,7 +34,8 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, long long q_stride, cons
                               const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ token_row,
                               const int* __restrict__ positions, T* __restrict__ out, long long out_stride, int n_tokens,
                               int nh, int nkv, int hd, int vd, int page_size, long long num_pages, float scale,
-                              float softcap, int window, int R, int* status) {
+                              float softcap, int window, int R, int* status, int keep_first, int values_are_keys,
+                              const float* gate, long long gate_stride) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * WARPS + warp;
@@ -49,8 +57,11 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, long long q_stride, cons
   const int pos = positions[t];
   const int* bt = block_tables + (long long)row * bt_stride;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const long long plane = (long long)nkv * page_size * hd;     // a page's keys, then its values
-  const long long page_elems = (long long)nkv * page_size * (hd + vd);
+  const long long plane = values_are_keys ? 0 : (long long)nkv * page_size * hd;     // a page's keys, then its values
+  const long long page_elems = (long long)nkv * page_size * (values_are_keys ? hd : hd + vd);
+  // positions below `kept` are seen although the window has passed them
+  const int kept = min(keep_first, lo);
+  const int first_c = lo / 32, kept_c = kept > 0 ? (kept + 31) / 32 : 0;
   const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
 
   float m = -INFINITY, l = 0.f;
@@ -58,9 +69,10 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, long long q_stride, cons
 #pragma unroll
   for (int i = 0; i < MAX_HD / 32; ++i) acc[i] = 0.f;
 
-  for (int c = lo / 32; c * 32 <= pos; ++c) {
+  for (int c = kept_c > 0 ? 0 : first_c; c * 32 <= pos; ++c) {
+    if (c >= kept_c && c < first_c) c = first_c;            // from the kept tokens straight to the window
     const int j = c * 32 + lane;
-    bool valid = j >= lo && j <= pos;
+    bool valid = (j >= lo || j < kept) && j <= pos;
     float s = -INFINITY;
     long long vbase = 0;
     if (valid) {
@@ -102,19 +114,25 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, long long q_stride, cons
 #pragma unroll
   for (int i = 0; i < MAX_HD / 32; ++i) {
     const int e = lane + 32 * i;
-    if (e < vd) op[e] = from_f<T>(acc[i] * inv);
+    if (e < vd) {
+      float o = acc[i] * inv;
+      if (gate != nullptr) o *= 1.0f / (1.0f + expf(-gate[(long long)t * gate_stride + (long long)h * vd + e]));
+      op[e] = from_f<T>(o);
+    }
   }
 }
 }  // namespace
 
 // q_dtype: the queries' type (FMX_F32 beside a bfloat16 cache, or the cache's own); dtype: the type of the
 // cache and of the output; hd / vd: head sizes of keys and values; softcap <= 0: scores are not capped.
-FMX_EXPORT int fmx_paged_attention_general(const void* q, long long q_stride, int q_dtype, const void* kv,
-                                           const int* block_tables, int bt_stride, const int* token_row,
-                                           const int* positions, void* out, long long out_stride, int n_tokens, int nh,
-                                           int nkv, int hd, int vd, int page_size, long long num_pages, float scale,
-                                           float softcap, int window, int R, int dtype, int* status,
-                                           cudaStream_t stream) {
+// keep_first, values_are_keys, gate: see the head of the file (0, 0, null: none of them).
+FMX_EXPORT int fmx_paged_attention_masked(const void* q, long long q_stride, int q_dtype, const void* kv,
+                                          const int* block_tables, int bt_stride, const int* token_row,
+                                          const int* positions, void* out, long long out_stride, int n_tokens, int nh,
+                                          int nkv, int hd, int vd, int page_size, long long num_pages, float scale,
+                                          float softcap, int window, int R, int dtype, int* status, int keep_first,
+                                          int values_are_keys, const float* gate, long long gate_stride,
+                                          cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || vd <= 0 || page_size <= 0)
     return fmx_fail("fmx_paged_attention_general: bad sizes T=%d nh=%d nkv=%d hd=%d vd=%d page=%d", n_tokens, nh, nkv, hd,
@@ -128,7 +146,11 @@ FMX_EXPORT int fmx_paged_attention_general(const void* q, long long q_stride, in
 #define FMX_ATTN_SIMPLE(TQ, T)                                                                                        \
   paged_attention_simple_kernel<TQ, T><<<(unsigned)grid, WARPS * 32, smem, stream>>>(                                 \
       (const TQ*)q, q_stride, (const T*)kv, block_tables, bt_stride, token_row, positions, (T*)out, out_stride, n_tokens, \
-      nh, nkv, hd, vd, page_size, num_pages, scale, softcap, window, R, status)
+      nh, nkv, hd, vd, page_size, num_pages, scale, softcap, window, R, status, keep_first, values_are_keys, gate,        \
+      gate_stride)
+  if (values_are_keys && hd != vd) return fmx_fail("fmx_paged_attention_general: values that are the keys have the keys' width");
+  if (keep_first < 0 || (gate != nullptr && gate_stride < (long long)nh * vd))
+    return fmx_fail("fmx_paged_attention_general: bad keep_first %d or gate rows too narrow", keep_first);
   if (dtype == FMX_F32 && q_dtype == FMX_F32)
     FMX_ATTN_SIMPLE(float, float);
   else if (dtype == FMX_BF16 && q_dtype == FMX_BF16)
@@ -140,6 +162,17 @@ FMX_EXPORT int fmx_paged_attention_general(const void* q, long long q_stride, in
 #undef FMX_ATTN_SIMPLE
   FMX_LAUNCH_CHECK();
   return 0;
+}
+
+FMX_EXPORT int fmx_paged_attention_general(const void* q, long long q_stride, int q_dtype, const void* kv,
+                                           const int* block_tables, int bt_stride, const int* token_row,
+                                           const int* positions, void* out, long long out_stride, int n_tokens, int nh,
+                                           int nkv, int hd, int vd, int page_size, long long num_pages, float scale,
+                                           float softcap, int window, int R, int dtype, int* status,
+                                           cudaStream_t stream) {
+  return fmx_paged_attention_masked(q, q_stride, q_dtype, kv, block_tables, bt_stride, token_row, positions, out, out_stride,
+                                    n_tokens, nh, nkv, hd, vd, page_size, num_pages, scale, softcap, window, R, dtype, status,
+                                    0, 0, nullptr, 0, stream);
 }
 
 FMX_EXPORT int fmx_paged_attention_simple(const void* q, long long q_stride, const void* kv, const int* block_tables,

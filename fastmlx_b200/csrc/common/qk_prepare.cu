@@ -1,8 +1,11 @@
 // Queries and keys made ready for attention in one pass: rotary positions on the first `rot`
 // dimensions of every head, then (optionally) each head divided by its root mean square, then
-// the keys and values written into the layer's pages.
+// the keys and values written into the layer's pages.  With `norm_first` the order is the other
+// one: a head is divided by its root mean square (and multiplied by a weight of hd values, one for
+// the queries and one for the keys, shared by their heads) and rotated after that.
 //
-// qkv is [T, nh*hd + nkv*hd + nkv*vd] as the projection left it (biases added).  The queries
+// qkv is [T, nh*hd + nkv*hd + nkv*vd] as the projection left it, of its own type (a product that
+// leaves in 32-bit feeds a bfloat16 cache); `bias`, if given, is added here, in 32-bit.  The queries
 // leave in 32-bit, [T, nh*hd]: scores are then taken from unrounded queries.  Keys and values go
 // to slot_mapping[t] of a cache whose pages hold [nkv, page_size, hd] keys followed by
 // [nkv, page_size, vd] values.  Angles (position * inv_freq[j]), sines, cosines, the sum of
@@ -13,11 +16,13 @@
 namespace {
 constexpr int QKP_WARPS = 4;
 
-template <typename T>
+template <typename TI, typename T>
 __global__ void __launch_bounds__(QKP_WARPS * 32)
-qk_prepare_kernel(const T* qkv, long long row_stride, const int* positions, const float* __restrict__ inv_freq,
+qk_prepare_kernel(const TI* qkv, long long row_stride, const int* positions, const float* __restrict__ inv_freq,
                   const long long* slot_mapping, float* q_out, T* kv, int nh, int nkv, int hd, int vd, int rot,
-                  int interleaved, float norm_eps, int page_size, long long num_pages, int* status) {
+                  int interleaved, float norm_eps, int page_size, long long num_pages, int* status,
+                  const float* __restrict__ bias, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                  int norm_first) {
   extern __shared__ float smem[];               // [rot/2] sines, [rot/2] cosines, then a head per warp
   pdl_wait();
   pdl_trigger();
@@ -27,7 +32,7 @@ qk_prepare_kernel(const T* qkv, long long row_stride, const int* positions, cons
   float* sn = smem;
   float* cs = smem + half;
   float* buf = smem + rot + warp * hd;
-  const T* row = qkv + (long long)t * row_stride;
+  const TI* row = qkv + (long long)t * row_stride;
   const float pos = (float)positions[t];
   for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &sn[j], &cs[j]);
   long long slot = (kv != nullptr && slot_mapping != nullptr) ? slot_mapping[t] : -1;
@@ -40,8 +45,18 @@ qk_prepare_kernel(const T* qkv, long long row_stride, const int* positions, cons
   const long long page_elems = (long long)nkv * page_size * (hd + vd);
   __syncthreads();
   for (int h = warp; h < nh + nkv; h += QKP_WARPS) {
-    const T* src = row + (long long)h * hd;
-    for (int e = lane; e < hd; e += 32) buf[e] = to_f(src[e]);
+    const TI* src = row + (long long)h * hd;
+    const float* hw = h < nh ? q_weight : k_weight;
+    float ss0 = 0.f;
+    for (int e = lane; e < hd; e += 32) {
+      const float v = to_f(src[e]) + (bias != nullptr ? bias[(long long)h * hd + e] : 0.f);
+      buf[e] = v;
+      ss0 = fmaf(v, v, ss0);
+    }
+    if (norm_first && norm_eps >= 0.f) {
+      const float m0 = 1.0f / sqrtf(warp_sum(ss0) / (float)hd + norm_eps);
+      for (int e = lane; e < hd; e += 32) buf[e] = buf[e] * m0 * (hw != nullptr ? hw[e] : 1.0f);
+    }
     __syncwarp();
     float ss = 0.f;
     float val[8];                               // head sizes up to 256
@@ -66,7 +81,16 @@ qk_prepare_kernel(const T* qkv, long long row_stride, const int* positions, cons
       val[i] = v;
     }
     float mul = 1.0f;
-    if (norm_eps >= 0.f) mul = 1.0f / sqrtf(warp_sum(ss) / (float)hd + norm_eps);
+    if (!norm_first && norm_eps >= 0.f) {
+      mul = 1.0f / sqrtf(warp_sum(ss) / (float)hd + norm_eps);
+      if (hw != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int e = lane + 32 * i;
+          if (e < hd) val[i] *= hw[e];
+        }
+      }
+    }
     if (h < nh) {
       float* dst = q_out + ((long long)t * nh + h) * hd;
 #pragma unroll
@@ -85,37 +109,51 @@ qk_prepare_kernel(const T* qkv, long long row_stride, const int* positions, cons
     __syncwarp();
   }
   if (slot < 0) return;
-  const T* vsrc = row + (long long)(nh + nkv) * hd;
+  const TI* vsrc = row + (long long)(nh + nkv) * hd;
+  const float* vbias = bias != nullptr ? bias + (long long)(nh + nkv) * hd : nullptr;
   T* vdst = kv + page * page_elems + (long long)nkv * page_size * hd;
   for (int it = threadIdx.x; it < nkv * vd; it += blockDim.x) {
     const int g = it / vd, e = it - g * vd;
-    vdst[((long long)g * page_size + off) * vd + e] = vsrc[it];
+    vdst[((long long)g * page_size + off) * vd + e] = from_f<T>(to_f(vsrc[it]) + (vbias != nullptr ? vbias[it] : 0.f));
   }
 }
 }  // namespace
 
 // rot = 0: nothing is rotated; norm_eps < 0: heads are not normalised; kv or slot_mapping null:
-// nothing is stored (a layer that reads another's cache then passes nkv = 0 as well).
-FMX_EXPORT int fmx_qk_prepare(const void* qkv, long long row_stride, const int* positions, const float* inv_freq,
-                              const long long* slot_mapping, float* q_out, void* kv, int T, int nh, int nkv, int hd, int vd,
-                              int rot, int interleaved, float norm_eps, int page_size, long long num_pages, int dtype,
-                              int* status, cudaStream_t stream) {
+// nothing is stored (a layer that reads another's cache then passes nkv = 0 as well).  in_dtype: the
+// type of qkv; dtype: the cache's.  bias (the whole row's, 32-bit), q_weight, k_weight may be null.
+FMX_EXPORT int fmx_qk_prepare_ex(const void* qkv, long long row_stride, const int* positions, const float* inv_freq,
+                                 const long long* slot_mapping, float* q_out, void* kv, int T, int nh, int nkv, int hd,
+                                 int vd, int rot, int interleaved, float norm_eps, int page_size, long long num_pages,
+                                 int in_dtype, int dtype, const float* bias, const float* q_weight, const float* k_weight,
+                                 int norm_first, int* status, cudaStream_t stream) {
   if (T == 0) return 0;
   if (T < 0 || nh < 0 || nkv < 0 || hd <= 0 || vd <= 0 || hd > 256 || rot < 0 || rot > hd || (rot & 1) || page_size <= 0)
     return fmx_fail("fmx_qk_prepare: bad sizes T=%d nh=%d nkv=%d hd=%d vd=%d rot=%d", T, nh, nkv, hd, vd, rot);
   if (rot > 0 && inv_freq == nullptr) return fmx_fail("fmx_qk_prepare: rot=%d needs a frequency table", rot);
   if (row_stride < (long long)(nh + nkv) * hd + (long long)nkv * vd) return fmx_fail("fmx_qk_prepare: row stride too small");
   const size_t smem = ((size_t)rot + (size_t)QKP_WARPS * hd) * sizeof(float);
-  if (dtype == FMX_F32)
-    fmx_launch(qk_prepare_kernel<float>, dim3(T), dim3(QKP_WARPS * 32), smem, stream, (const float*)qkv, row_stride,
-               positions, inv_freq, slot_mapping, q_out, (float*)kv, nh, nkv, hd, vd, rot, interleaved, norm_eps, page_size,
-               num_pages, status);
-  else if (dtype == FMX_BF16)
-    fmx_launch(qk_prepare_kernel<bf16>, dim3(T), dim3(QKP_WARPS * 32), smem, stream, (const bf16*)qkv, row_stride, positions,
-               inv_freq, slot_mapping, q_out, (bf16*)kv, nh, nkv, hd, vd, rot, interleaved, norm_eps, page_size, num_pages,
-               status);
+#define FMX_QKP(TI, TKV)                                                                                                  \
+  fmx_launch(qk_prepare_kernel<TI, TKV>, dim3(T), dim3(QKP_WARPS * 32), smem, stream, (const TI*)qkv, row_stride, positions, \
+             inv_freq, slot_mapping, q_out, (TKV*)kv, nh, nkv, hd, vd, rot, interleaved, norm_eps, page_size, num_pages,  \
+             status, bias, q_weight, k_weight, norm_first)
+  if (in_dtype == FMX_F32 && dtype == FMX_F32)
+    FMX_QKP(float, float);
+  else if (in_dtype == FMX_BF16 && dtype == FMX_BF16)
+    FMX_QKP(bf16, bf16);
+  else if (in_dtype == FMX_F32 && dtype == FMX_BF16)
+    FMX_QKP(float, bf16);
   else
-    return fmx_fail("fmx_qk_prepare: unknown dtype %d", dtype);
+    return fmx_fail("fmx_qk_prepare: no kernel for an input of type %d and a cache of type %d", in_dtype, dtype);
+#undef FMX_QKP
   FMX_LAUNCH_CHECK();
   return 0;
+}
+
+FMX_EXPORT int fmx_qk_prepare(const void* qkv, long long row_stride, const int* positions, const float* inv_freq,
+                              const long long* slot_mapping, float* q_out, void* kv, int T, int nh, int nkv, int hd, int vd,
+                              int rot, int interleaved, float norm_eps, int page_size, long long num_pages, int dtype,
+                              int* status, cudaStream_t stream) {
+  return fmx_qk_prepare_ex(qkv, row_stride, positions, inv_freq, slot_mapping, q_out, kv, T, nh, nkv, hd, vd, rot, interleaved,
+                           norm_eps, page_size, num_pages, dtype, dtype, nullptr, nullptr, nullptr, 0, status, stream);
 }

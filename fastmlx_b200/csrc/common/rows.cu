@@ -1,0 +1,95 @@
+// Two small row-wise kernels that mixers with a latent or a gate need.
+//
+// rmsnorm_rows: a slice of every row divided by its root mean square and multiplied by a weight, x / sqrt(mean(x^2)
+// + eps) * w, in 32-bit, written either to the same row of a dense output or to the row that a map names (the
+// cache slot of the token: how a normalised latent goes straight into its page).  The sum of squares is taken in an
+// order that depends on the slice's width alone.
+//
+// sigmoid_gate: o[t, j] *= sigmoid(g[t, j / group]) in 32-bit: group = 1 gates element by element, group = the
+// head's width gates a head by one value.
+#include <math.h>
+#include "common.cuh"
+
+namespace {
+constexpr int NORM_BLOCK = 128;
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(NORM_BLOCK)
+rmsnorm_rows_kernel(const TI* x, long long x_stride, const float* __restrict__ w, float eps, TO* out, long long out_stride,
+                    const long long* row_map, long long max_rows, int n, int* status) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const TI* src = x + (long long)t * x_stride;
+  float ss = 0.f;
+  for (int e = threadIdx.x; e < n; e += NORM_BLOCK) {
+    const float v = to_f(src[e]);
+    ss = fmaf(v, v, ss);
+  }
+  const float mul = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ss) / (float)n + eps);
+  long long row = t;
+  if (row_map != nullptr) {
+    row = row_map[t];
+    if (row < 0) return;                         // a token that is stored nowhere (a padding row)
+    if (row >= max_rows) {
+      if (threadIdx.x == 0) fmx_set_status(status, FMX_BAD_SLOT, row, t);
+      return;
+    }
+  }
+  TO* dst = out + row * out_stride;
+  for (int e = threadIdx.x; e < n; e += NORM_BLOCK) dst[e] = from_f<TO>(to_f(src[e]) * mul * w[e]);
+}
+
+template <typename TO, typename TG>
+__global__ void sigmoid_gate_kernel(TO* o, long long o_stride, const TG* g, long long g_stride, long long rows, int cols,
+                                    int group) {
+  pdl_wait();
+  pdl_trigger();
+  const long long n = rows * cols;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / cols;
+    const int c = (int)(idx - r * cols);
+    const float z = to_f(g[r * g_stride + c / group]);
+    TO* p = o + r * o_stride + c;
+    *p = from_f<TO>(to_f(*p) / (1.0f + expf(-z)));
+  }
+}
+}  // namespace
+
+// row_map null: row t of the output; else row row_map[t] (below max_rows; a negative entry is skipped).
+FMX_EXPORT int fmx_rmsnorm_rows(const void* x, long long x_stride, int x_dtype, const float* w, float eps, void* out,
+                                long long out_stride, int out_dtype, const long long* row_map, long long max_rows, int rows,
+                                int n, int* status, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (rows < 0 || n <= 0 || x_stride < n || out_stride < n) return fmx_fail("fmx_rmsnorm_rows: bad sizes rows=%d n=%d", rows, n);
+#define FMX_NR(TI, TO)                                                                                                  \
+  fmx_launch(rmsnorm_rows_kernel<TI, TO>, dim3(rows), dim3(NORM_BLOCK), 0, stream, (const TI*)x, x_stride, w, eps, (TO*)out, \
+             out_stride, row_map, max_rows, n, status)
+  if (x_dtype == FMX_F32 && out_dtype == FMX_F32) FMX_NR(float, float);
+  else if (x_dtype == FMX_F32 && out_dtype == FMX_BF16) FMX_NR(float, bf16);
+  else if (x_dtype == FMX_BF16 && out_dtype == FMX_BF16) FMX_NR(bf16, bf16);
+  else if (x_dtype == FMX_BF16 && out_dtype == FMX_F32) FMX_NR(bf16, float);
+  else return fmx_fail("fmx_rmsnorm_rows: unknown dtypes %d, %d", x_dtype, out_dtype);
+#undef FMX_NR
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
+FMX_EXPORT int fmx_sigmoid_gate(void* o, long long o_stride, int o_dtype, const void* g, long long g_stride, int g_dtype,
+                                int rows, int cols, int group, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return 0;
+  if (rows < 0 || cols < 0 || group <= 0 || o_stride < cols) return fmx_fail("fmx_sigmoid_gate: bad sizes rows=%d cols=%d group=%d", rows, cols, group);
+  const long long n = (long long)rows * cols, cap = (long long)fmx_num_sms() * 16;
+  const int block = 256;
+  const int grid = (int)((n + block - 1) / block < cap ? (n + block - 1) / block : cap);
+#define FMX_SG(TO, TG)                                                                                                \
+  fmx_launch(sigmoid_gate_kernel<TO, TG>, dim3(grid), dim3(block), 0, stream, (TO*)o, o_stride, (const TG*)g, g_stride, \
+             (long long)rows, cols, group)
+  if (o_dtype == FMX_F32 && g_dtype == FMX_F32) FMX_SG(float, float);
+  else if (o_dtype == FMX_BF16 && g_dtype == FMX_F32) FMX_SG(bf16, float);
+  else if (o_dtype == FMX_BF16 && g_dtype == FMX_BF16) FMX_SG(bf16, bf16);
+  else return fmx_fail("fmx_sigmoid_gate: unknown dtypes %d, %d", o_dtype, g_dtype);
+#undef FMX_SG
+  FMX_LAUNCH_CHECK();
+  return 0;
+}

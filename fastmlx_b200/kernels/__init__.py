@@ -321,42 +321,55 @@ def paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> t
 
 
 def qk_prepare(qkv, positions, inv_freq, rotary_dim, traditional, norm_eps, slot_mapping, kv, nh, nkv, hd, vd,
-               status) -> torch.Tensor:
+               status, bias=None, q_weight=None, k_weight=None, norm_first: bool = False) -> torch.Tensor:
     """Queries and keys of qkv[T, nh*hd + nkv*hd + nkv*vd] made ready for attention: rotated over their
     first `rotary_dim` dimensions, then (norm_eps not None) each head divided by its root mean square;
     keys and values are stored at slot_mapping in pages that hold [nkv, page, hd] keys and then
-    [nkv, page, vd] values.  -> the queries in 32-bit, [T, nh*hd]."""
-    _need_cuda(qkv, positions, inv_freq, slot_mapping, kv)
+    [nkv, page, vd] values.  -> the queries in 32-bit, [T, nh*hd].  qkv may be of another type than the
+    cache (a product that leaves in 32-bit beside bfloat16 pages).  `bias` (32-bit, a whole row's) is added
+    first; `q_weight` / `k_weight` ([hd], 32-bit) multiply the normalised heads; `norm_first` normalises
+    before the rotation instead of after it."""
+    _need_cuda(qkv, positions, inv_freq, slot_mapping, kv, bias, q_weight, k_weight)
     assert qkv.dim() == 2 and qkv.stride(1) == 1 and positions.dtype == torch.int32
     T = qkv.shape[0]
     q = torch.empty((T, nh * hd), dtype=torch.float32, device=qkv.device)
     if kv is not None:
-        assert kv.is_contiguous() and kv.dtype == qkv.dtype and slot_mapping is not None and slot_mapping.dtype == torch.int64
+        assert kv.is_contiguous() and slot_mapping is not None and slot_mapping.dtype == torch.int64
         num_pages = kv.shape[0]
         page_size = kv[0].numel() // (nkv * (hd + vd))
     else:
         num_pages, page_size = 0, 1
-    call("common", "fmx_qk_prepare", qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), _ptr(inv_freq), _ptr(slot_mapping),
-         q.data_ptr(), _ptr(kv), T, nh, nkv if kv is not None else 0, hd, vd, int(rotary_dim), int(bool(traditional)),
-         -1.0 if norm_eps is None else float(norm_eps), page_size, num_pages, _dt(qkv), _ptr(status), _stream())
+    for v in (bias, q_weight, k_weight):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous())
+    call("common", "fmx_qk_prepare_ex", qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), _ptr(inv_freq),
+         _ptr(slot_mapping), q.data_ptr(), _ptr(kv), T, nh, nkv if kv is not None else 0, hd, vd, int(rotary_dim),
+         int(bool(traditional)), -1.0 if norm_eps is None else float(norm_eps), page_size, num_pages, _dt(qkv),
+         _dt(kv) if kv is not None else _dt(qkv), _ptr(bias), _ptr(q_weight), _ptr(k_weight), int(bool(norm_first)),
+         _ptr(status), _stream())
     return q
 
 
-def paged_attention_general(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, window, page_size, out=None) -> torch.Tensor:
+def paged_attention_general(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, window, page_size, out=None,
+                            keep_first: int = 0, values_are_keys: bool = False, gate=None) -> torch.Tensor:
     """Attention with 32-bit scores and weights, one warp per (token, head): queries q[T, nh*hd] of their own
     type over pages of [nkv, page, hd] keys and [nkv, page, vd] values; scores are capped by
-    softcap * tanh(s / softcap) where softcap > 0.  `out` may be a slice of a wider buffer.  -> [T, nh*vd]."""
-    _need_cuda(q, kv)
+    softcap * tanh(s / softcap) where softcap > 0.  `out` may be a slice of a wider buffer.  -> [T, nh*vd].
+    `keep_first`: beside a window, a request's first tokens that stay visible; `values_are_keys`: pages of keys
+    only, which are the values too; `gate` (32-bit [T, nh*vd], rows may be a slice): the output is multiplied
+    element by element with sigmoid(gate)."""
+    _need_cuda(q, kv, gate)
     assert kv.is_contiguous() and q.stride(1) == 1
     T = q.shape[0]
     if out is None:
         out = torch.empty((T, nh * vd), dtype=kv.dtype, device=q.device)
     assert out.dtype == kv.dtype and out.stride(1) == 1 and out.shape == (T, nh * vd)
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (T, nh * vd))
     bt = group.block_tables
-    call("common", "fmx_paged_attention_general", q.data_ptr(), q.stride(0), _dt(q), kv.data_ptr(), bt.data_ptr(),
+    call("common", "fmx_paged_attention_masked", q.data_ptr(), q.stride(0), _dt(q), kv.data_ptr(), bt.data_ptr(),
          bt.stride(0), ctx.token_row.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), out.stride(0), T, nh, nkv, hd, vd,
          int(page_size), kv.shape[0], float(scale), float(softcap or 0.0), int(window), bt.shape[0], _dt(kv),
-         _ptr(ctx.status), _stream())
+         _ptr(ctx.status), int(keep_first), int(bool(values_are_keys)), _ptr(gate), gate.stride(0) if gate is not None else 0,
+         _stream())
     return out
 
 
@@ -470,6 +483,115 @@ def gated_rmsnorm(o, gate, weight, eps, H, Dv, out_dtype, out=None) -> torch.Ten
     assert gate.stride(1) == 1 and out.stride(1) == 1 and gate.dtype == out.dtype and o.is_contiguous()
     call("common", "fmx_gated_rmsnorm", o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(), out.data_ptr(),
          out.stride(0), T, H, Dv, float(eps), _dt(out), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- dynamic tanh, latents, gates, routed experts
+def dyt_step(y, post, mult, add, residual, pre, out_dtype, out=None, keep_stream: bool = True):
+    """One pass over the stream: residual <- residual + mult * post(y) + add, out = pre(residual), all 32-bit.
+    post and pre are (alpha, weight, bias) of a dynamic tanh, tanh(alpha x) weight + bias, or None for the identity;
+    y (bfloat16 or 32-bit, rows may be a slice) may be None, `add` (a 32-bit vector) too; residual None: the stream
+    starts at zero and gets an array of its own; pre False: nothing but the stream is written.  `out` may be a
+    slice of a wider buffer.  -> (out or None, residual)."""
+    ref = y if y is not None else residual
+    _need_cuda(y, residual, add, out)
+    assert ref is not None and ref.dim() == 2 and (y is None or y.stride(1) == 1)
+    rows, cols = ref.shape
+    assert residual is None or (residual.dtype == torch.float32 and residual.is_contiguous() and residual.shape == ref.shape)
+    res_in = residual
+    if residual is None:
+        residual = torch.empty((rows, cols), dtype=torch.float32, device=ref.device)
+    want_out = pre is not False
+    if want_out and out is None:
+        out = torch.empty((rows, cols), dtype=out_dtype, device=ref.device)
+    pa, pw, pb = post if post else (0.0, None, None)
+    qa, qw, qb = pre if pre else (0.0, None, None)
+    call("common", "fmx_dyt_step", _ptr(y), y.stride(0) if y is not None else 0, _dt(y) if y is not None else F32, float(pa),
+         _ptr(pw), _ptr(pb), float(mult), _ptr(add), _ptr(res_in), residual.data_ptr() if keep_stream else None, float(qa),
+         _ptr(qw), _ptr(qb), _ptr(out) if want_out else None, out.stride(0) if want_out else 0,
+         _dt(out) if want_out else F32, rows, cols, _stream())
+    return (out if want_out else None), residual
+
+
+def rmsnorm_rows(x, weight, eps, out=None, out_dtype=None, row_map=None, status=None):
+    """x[T, n] (rows may be a slice) / sqrt(mean(x^2) + eps) * weight, in 32-bit, into `out` (a dense array, or any
+    array of rows of n where `row_map`, int64 [T], names each token's row: a cache of latents addressed by slot)."""
+    _need_cuda(x, weight, out, row_map)
+    assert x.dim() == 2 and x.stride(1) == 1 and weight.dtype == torch.float32
+    T, n = x.shape
+    if out is None:
+        out = torch.empty((T, n), dtype=out_dtype or x.dtype, device=x.device)
+    if row_map is not None:
+        assert row_map.dtype == torch.int64 and out.is_contiguous() and out.numel() % n == 0
+        max_rows, stride = out.numel() // n, n
+    else:
+        assert out.shape == (T, n) and out.stride(1) == 1
+        max_rows, stride = T, out.stride(0)
+    call("common", "fmx_rmsnorm_rows", x.data_ptr(), x.stride(0), _dt(x), weight.data_ptr(), float(eps), out.data_ptr(), stride,
+         _dt(out), _ptr(row_map), max_rows, T, n, _ptr(status), _stream())
+    return out
+
+
+def sigmoid_gate(o, gate, group: int = 1):
+    """o[t, j] *= sigmoid(gate[t, j // group]) in place, in 32-bit; rows of either may be slices."""
+    _need_cuda(o, gate)
+    assert o.dim() == 2 and o.stride(1) == 1 and gate.stride(1) == 1 and gate.shape[1] * group == o.shape[1]
+    call("common", "fmx_sigmoid_gate", o.data_ptr(), o.stride(0), _dt(o), gate.data_ptr(), gate.stride(0), _dt(gate), o.shape[0],
+         o.shape[1], int(group), _stream())
+    return o
+
+
+def moe_route(logits, top: int, groups: int = 1, keep: int = 1, want_chosen: bool = False):
+    """Router logits [T, E] (32-bit) -> weights [T, E] (32-bit): the softmax score where an expert is among the token's
+    `top` best of the `keep` best groups (of `groups` groups of neighbours, each scored by its best member), else zero;
+    not renormalised.  With `want_chosen` also the chosen indices, int32 [T, top]."""
+    _need_cuda(logits)
+    assert logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1
+    T, E = logits.shape
+    w = torch.empty((T, E), dtype=torch.float32, device=logits.device)
+    chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device) if want_chosen else None
+    call("common", "fmx_moe_route", logits.data_ptr(), logits.stride(0), T, E, int(top), int(groups), int(keep), w.data_ptr(),
+         _ptr(chosen), _stream())
+    return (w, chosen) if want_chosen else w
+
+
+def moe_expert_act(gu, weights, E: int, ff: int, limit: float, limit_shared: float = 0.0, out=None):
+    """The experts' hidden layers side by side: gu[T, 2F] holds F gates then F ups, F = E*ff + the shared expert's
+    width; -> [T, F]: w * g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit), w the
+    token's weight for the column's expert (1 for the shared columns at the end), zero where it chose it not."""
+    _need_cuda(gu, weights)
+    assert gu.dim() == 2 and gu.stride(1) == 1 and gu.shape[1] % 2 == 0 and weights.dtype == torch.float32
+    T, F = gu.shape[0], gu.shape[1] // 2
+    assert weights.shape == (T, E) and weights.is_contiguous()
+    if out is None:
+        out = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
+    call("common", "fmx_moe_expert_act", gu.data_ptr(), gu.stride(0), weights.data_ptr(), out.data_ptr(), out.stride(0), T,
+         int(E), int(ff), F, float(limit), float(limit_shared), _dt(gu), _stream())
+    return out
+
+
+def head_linear(x, w, out_dtype) -> torch.Tensor:
+    """A product per head: x[T, H*K] (head by head, rows may be a slice) and w[H, N, K] -> [T, H*N], out[t, h] =
+    w[h] x[t, h], accumulated in 32-bit.  bfloat16 operands go to the library's batched product; 32-bit ones to
+    the fixed-order kernel, head by head."""
+    _need_cuda(x, w)
+    H, N, K = w.shape
+    T = x.shape[0]
+    assert x.dim() == 2 and x.shape[1] == H * K and x.stride(1) == 1 and w.is_contiguous()
+    out = torch.empty((T, H * N), dtype=out_dtype, device=x.device)
+    if T == 0:
+        return out
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        a = x.as_strided((H, T, K), (K, x.stride(0), 1))
+        o = out.as_strided((H, T, N), (N, H * N, 1))
+        if out_dtype == torch.bfloat16:
+            torch.bmm(a, w.transpose(1, 2), out=o)
+        else:
+            o.copy_(torch.bmm(a, w.transpose(1, 2), out_dtype=out_dtype))
+        return out
+    for h in range(H):
+        call("common", "fmx_gemm_simple", x.data_ptr() + h * K * x.element_size(), w[h].data_ptr(), None,
+             out.data_ptr() + h * N * out.element_size(), T, N, K, x.stride(0), K, H * N, _dt(x), _dt(w), _dt(out), _stream())
     return out
 
 

@@ -40,6 +40,15 @@ _SIGNATURES = {
         "fmx_delta_rule": [_P, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "fmx_gated_rmsnorm": [_P, _P, _L, _P, _P, _L, _I, _I, _I, _F, _I, _P],
         "fmx_activation": [_P, _L, _P, _L, _I, _I, _I, _I, _P],
+        "fmx_paged_attention_masked": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _L, _F, _F, _I, _I,
+                                       _I, _P, _I, _I, _P, _L, _P],
+        "fmx_qk_prepare_ex": [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _L, _I, _I, _P, _P, _P, _I, _P,
+                              _P],
+        "fmx_dyt_step": [_P, _L, _I, _F, _P, _P, _F, _P, _P, _P, _F, _P, _P, _P, _L, _I, _I, _I, _P],
+        "fmx_rmsnorm_rows": [_P, _L, _I, _P, _F, _P, _L, _I, _P, _L, _I, _I, _P, _P],
+        "fmx_sigmoid_gate": [_P, _L, _I, _P, _L, _I, _I, _I, _I, _P],
+        "fmx_moe_route": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P],
+        "fmx_moe_expert_act": [_P, _L, _P, _P, _L, _I, _I, _I, _I, _F, _F, _I, _P],
     },
     "bf16": {
         "fmx_gemv": [_P, _L, _P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P],

@@ -1,15 +1,19 @@
 from .attention import GQAAttention
 from .base import (FeedForward, Mixer, Norm, PagedKVSpec, Part, PositionEncoding, Run, Runtime,
                    StateSpec, StreamEncoding, WeightSpec)
-from .block import ParallelBlock, PreNormBlock
+from .block import ParallelBlock, PreNormBlock, SandwichBlock
 from .delta import GatedDeltaMixer
 from .embedding import Embedding, LMHead
 from .linear import JoinedLinear, Linear
 from .mlp import DenseMLP, SwiGLU
 from .model import Model
-from .norm import RMSNorm
+from .latent import LatentAttention
+from .loop import LoopInput, LoopPass
+from .moe import RoutedExperts
+from .norm import DynamicTanh, Pending, RMSNorm
 from .rope import NoPositionEncoding, RotaryEmbedding, inverse_frequencies
 
 __all__ = ["GQAAttention", "FeedForward", "Mixer", "Norm", "PagedKVSpec", "Part", "PositionEncoding",
            "Run", "Runtime", "StateSpec", "StreamEncoding", "WeightSpec", "PreNormBlock", "Embedding", "LMHead", "Linear",
-           "SwiGLU", "DenseMLP", "JoinedLinear", "ParallelBlock", "GatedDeltaMixer", "Model", "RMSNorm", "NoPositionEncoding", "RotaryEmbedding", "inverse_frequencies"]
+           "SwiGLU", "DenseMLP", "JoinedLinear", "ParallelBlock", "GatedDeltaMixer", "Model", "RMSNorm", "NoPositionEncoding", "RotaryEmbedding", "inverse_frequencies", "SandwichBlock", "LatentAttention", "LoopInput", "LoopPass", "RoutedExperts",
+           "DynamicTanh", "Pending"]

@@ -1,7 +1,9 @@
 """Grouped-query attention over a paged cache."""
 from __future__ import annotations
 
-from .base import Mixer, PagedKVSpec, PositionEncoding, Runtime
+import torch
+
+from .base import Mixer, PagedKVSpec, PositionEncoding, Runtime, WeightSpec, to_f32_vector
 from .linear import Linear
 
 
@@ -23,6 +25,14 @@ class GQAAttention(Mixer):
     (no weight); `v_head_dim` gives values another width than keys.  There the queries stay in
     32-bit from the rotation to the scores.  `output=False` leaves the output projection to the
     block (`out_piece` names its tensors), which may join it with the feed-forward's.
+
+    Further choices of that route.  `qk_norm_weights` = (name, name): the normalised q and k heads are multiplied
+    by a weight of head_dim values each, shared by the heads; `qk_norm_first`: q and k are normalised before the
+    rotation instead of after it.  `keep_first` k > 0 beside a window: a request's first k tokens stay visible to
+    every later query, at their true positions (the cache keeps their pages).  `gate` = a projection's name: the
+    heads' outputs are multiplied element by element with sigmoid(W_g x), W_g of the output's width, before the
+    output projection; it rides in the q/k/v product.  `late_bias`: the q/k/v product leaves in 32-bit and the
+    biases are added, in 32-bit, by the kernel that normalises and rotates (a gate has no bias).
     """
 
     supports_cuda_graph = True
@@ -32,14 +42,25 @@ class GQAAttention(Mixer):
                  window: int = 0, share_kv: bool = False,
                  proj_names=("q_proj", "k_proj", "v_proj", "o_proj"), v_head_dim: int | None = None,
                  softcap: float = 0.0, qk_norm_eps: float | None = None, output: bool = True,
-                 weight_suffix: str = ".weight", bias_suffix: str = ".bias"):
+                 weight_suffix: str = ".weight", bias_suffix: str = ".bias", qk_norm_weights=None,
+                 qk_norm_first: bool = False, keep_first: int = 0, gate: str | None = None, late_bias: bool = False,
+                 out_bias: bool | None = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are no multiple of {num_kv_heads} kv heads")
         self.nh, self.nkv, self.hd = int(num_heads), int(num_kv_heads), int(head_dim)
         self.vd = int(v_head_dim) if v_head_dim else self.hd
         self.softcap = float(softcap or 0.0)
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
-        self.general = self.softcap > 0 or self.qk_norm_eps is not None or self.vd != self.hd
+        self.qk_norm_weights = tuple(f"{name}.{n}" for n in qk_norm_weights) if qk_norm_weights else None
+        self.qk_norm_first, self.keep_first = bool(qk_norm_first), int(keep_first)
+        self.gate_name = f"{name}.{gate}" if gate else None
+        self.late_bias = bool(late_bias) and bool(bias)
+        if self.keep_first and not window:
+            self.keep_first = 0                         # without a window every token is seen anyway
+        if (self.qk_norm_weights or self.qk_norm_first) and self.qk_norm_eps is None:
+            raise ValueError("a weight or an order for the q/k norm needs its eps")
+        self.general = (self.softcap > 0 or self.qk_norm_eps is not None or self.vd != self.hd or self.keep_first > 0
+                        or self.gate_name is not None or self.late_bias)
         self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
         self.window = int(window)
         self.share_kv = bool(share_kv)
@@ -48,17 +69,38 @@ class GQAAttention(Mixer):
         outs = [(qn, self.nh * self.hd)]
         if not share_kv:
             outs += [(kn, self.nkv * self.hd), (vn, self.nkv * self.vd)]
-        self.qkv = Linear(width, outs, bias, weight_suffix=weight_suffix, bias_suffix=bias_suffix)
+        self.qkv_features = sum(o for _, o in outs)
+        self.bias_names = [(n + bias_suffix, o) for n, o in outs] if self.late_bias else []
         self.inner_features = self.nh * self.vd
-        self.out_piece = (on + weight_suffix, self.inner_features, on + bias_suffix if bias else None)
-        self.o = Linear(self.inner_features, [(on, width)], bias, weight_suffix=weight_suffix,
+        if self.gate_name:
+            outs = outs + [(self.gate_name, self.inner_features)]
+        self.qkv = Linear(width, outs, bias and not self.late_bias, weight_suffix=weight_suffix, bias_suffix=bias_suffix)
+        out_bias = bool(bias) if out_bias is None else bool(out_bias)
+        self.out_piece = (on + weight_suffix, self.inner_features, on + bias_suffix if out_bias else None)
+        self.o = Linear(self.inner_features, [(on, width)], out_bias, weight_suffix=weight_suffix,
                         bias_suffix=bias_suffix) if output else None
+        self.row_bias = self.q_weight = self.k_weight = None
 
     def children(self):
         return tuple(p for p in (self.qkv, self.o, self.pos) if p is not None)
 
+    def own_weight_specs(self):
+        specs = [WeightSpec(n, (o,), "bias") for n, o in self.bias_names]
+        if self.qk_norm_weights:
+            specs += [WeightSpec(n, (self.hd,), "norm") for n in self.qk_norm_weights]
+        return specs
+
+    def bind_own(self, tensors, rt: Runtime):
+        if self.bias_names:
+            self.row_bias = torch.cat([to_f32_vector(tensors[n], rt) for n, _ in self.bias_names]).contiguous()
+        if self.qk_norm_weights:
+            self.q_weight, self.k_weight = (to_f32_vector(tensors[n], rt) for n in self.qk_norm_weights)
+
+    def weight_bytes(self):
+        return super().weight_bytes() + 4 * (len(self.bias_names) and self.qkv_features)
+
     def cache_spec(self):
-        return PagedKVSpec(self.nkv, self.hd, self.window, 0 if self.vd == self.hd else self.vd)
+        return PagedKVSpec(self.nkv, self.hd, self.window, 0 if self.vd == self.hd else self.vd, self.keep_first)
 
     def forward(self, x, ctx, cache):
         return self.o.forward(self.forward_inner(x, ctx, cache))
@@ -66,7 +108,8 @@ class GQAAttention(Mixer):
     def forward_inner(self, x, ctx, cache, out=None):
         """The heads' outputs side by side, [T, nh * v width], before the output projection; into
         `out` (a slice of a wider buffer) where one is given."""
-        qkv = self.qkv.forward(x)
+        extended = self.late_bias or self.gate_name is not None
+        qkv = self.qkv.forward(x, out_dtype=torch.float32 if extended else None)
         if not self.general:
             res = self._attend(qkv, ctx, cache)
             if out is None:
@@ -78,7 +121,19 @@ class GQAAttention(Mixer):
         g = ctx.groups[cache.group]
         store = cache.writable and not self.share_kv
         q = k.qk_prepare(qkv, ctx.positions, inv_freq, rot, trad, self.qk_norm_eps, g.slot_mapping if store else None,
-                         cache.kv if store else None, self.nh, self.nkv, self.hd, self.vd, ctx.status)
+                         cache.kv if store else None, self.nh, self.nkv, self.hd, self.vd, ctx.status,
+                         **(dict(bias=self.row_bias, q_weight=self.q_weight, k_weight=self.k_weight,
+                                 norm_first=self.qk_norm_first) if extended or self.q_weight is not None or self.qk_norm_first
+                            else {}))
+        gate = qkv[:, self.qkv_features:] if self.gate_name else None
+        if extended or self.keep_first:
+            wide_ex = getattr(k, "wide_attention_takes", None)
+            if wide_ex is not None and wide_ex(q, cache.kv, self.hd, self.vd, out):
+                return k.paged_attention_wide(q, cache.kv, ctx, g, self.nh, self.nkv, self.hd, self.scale, self.softcap,
+                                              self.window, out=out, keep_first=self.keep_first, gate=gate)
+            return k.paged_attention_general(q, cache.kv, ctx, g, self.nh, self.nkv, self.hd, self.vd, self.scale,
+                                             self.softcap, self.window, g.page_size, out=out, keep_first=self.keep_first,
+                                             gate=gate)
         wide = getattr(k, "wide_attention_ok", None)
         if wide is not None and wide(q, cache.kv, self.hd, self.vd) and (out is None or (out.stride(0) % 2 == 0
                                                                                          and out.data_ptr() % 4 == 0)):

@@ -33,15 +33,26 @@ class PagedKVSpec:
     """A mixer that keeps keys and values of earlier tokens in pages.  `window` = 0
     keeps every key; w > 0 only the last w (the page manager gives older pages back).
     `v_head_dim` = 0: values are as wide as keys; else a page holds its keys
-    [kv heads, page, head_dim] followed by its values [kv heads, page, v_head_dim]."""
+    [kv heads, page, head_dim] followed by its values [kv heads, page, v_head_dim].
+    `keep_first` > 0 beside a window: the request's first keep_first tokens stay visible to
+    every later query, so the pages that hold them are never given back.  `values_are_keys`:
+    a page holds keys only and attention reads them as values too (a cached latent from which
+    both are read out)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
+    keep_first: int = 0
+    values_are_keys: bool = False
 
     @property
     def value_dim(self) -> int:
         return self.v_head_dim or self.head_dim
+
+    @property
+    def token_width(self) -> int:
+        """Elements one token holds per kv head."""
+        return self.head_dim if self.values_are_keys else self.head_dim + self.value_dim
 
 
 @dataclass(frozen=True)

@@ -5,6 +5,7 @@ import torch
 
 from .base import FeedForward, Mixer, Norm, Part
 from .linear import JoinedLinear
+from .norm import Pending
 
 
 class PreNormBlock(Part):
@@ -79,3 +80,44 @@ class ParallelBlock(Part):
         if self.ffn is not None:
             self.ffn.forward_inner(h, ctx, out=joined[:, m:])
         return self.out.forward(joined), residual
+
+
+class SandwichBlock(Part):
+    """x <- x + r * norm1b(mixer(norm1(x))); x <- x + r * norm2b(ffn(norm2(x))): a norm in front of and behind each
+    sublayer, and a multiplier r on what enters the stream.  `ffn` (with its two norms) may be None.
+
+    The block hands its last sublayer's output on as a `Pending` sum, so that the norm behind a sublayer, the
+    scaled sum into the 32-bit stream and the norm in front of the next sublayer are one kernel; its norms must
+    take a `Pending` (`DynamicTanh` does)."""
+
+    def __init__(self, mixer: Mixer, ffn: FeedForward | None, norm1: Norm, norm1b: Norm, norm2: Norm | None,
+                 norm2b: Norm | None, mult: float = 1.0):
+        self.mixer, self.ffn, self.mult = mixer, ffn, float(mult)
+        self.norm1, self.norm1b, self.norm2, self.norm2b = norm1, norm1b, norm2, norm2b
+        if ffn is not None and (norm2 is None or norm2b is None):
+            raise ValueError("a feed-forward needs the norms around it")
+
+    def children(self):
+        parts = [self.norm1, self.mixer, self.norm1b]
+        if self.ffn is not None:
+            parts += [self.norm2, self.ffn, self.norm2b]
+        return tuple(parts)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def state_spec(self):
+        return self.mixer.state_spec()
+
+    @property
+    def supports_cuda_graph(self):
+        return bool(getattr(self.mixer, "supports_cuda_graph", False)) and \
+            bool(getattr(self.ffn, "supports_cuda_graph", True))
+
+    def forward(self, delta, residual, ctx, cache):
+        h, residual = self.norm1.forward(delta, residual)
+        pending = Pending(self.mixer.forward(h, ctx, cache), self.norm1b, self.mult)
+        if self.ffn is None:
+            return pending, residual
+        h, residual = self.norm2.forward(pending, residual)
+        return Pending(self.ffn.forward(h, ctx), self.norm2b, self.mult), residual

@@ -7,7 +7,10 @@ import torch
 
 from ..weights.loader import WeightError
 from .base import Norm, Part, Run, Runtime
+from dataclasses import replace
+
 from .embedding import Embedding, LMHead
+from .norm import Pending
 
 
 class Model(Part):
@@ -95,12 +98,15 @@ class Model(Part):
         delta = self.embed.forward(ctx.tokens, ctx)
         if self.stream_encoding is not None:
             delta = self.stream_encoding.forward(delta, ctx)
+        ctx.scratch["embedding"] = delta              # a layer may read the embeddings again (the entry of a loop)
         residual = None
         for pos, run in enumerate(self.schedule):
             delta, residual = self.layers[run.layer].forward(delta, residual, ctx, ctx.caches[pos])
         k = self.rt.k
         if ctx.logit_rows is not None:
-            if delta is not None:
+            if isinstance(delta, Pending):                # a sum that the final norm's kernel will take
+                delta = replace(delta, x=k.gather_rows(delta.x, ctx.logit_rows, ctx.status))
+            elif delta is not None:
                 delta = k.gather_rows(delta, ctx.logit_rows, ctx.status)
             if residual is not None:
                 residual = k.gather_rows(residual, ctx.logit_rows, ctx.status)

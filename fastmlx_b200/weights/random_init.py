@@ -5,7 +5,7 @@ tamnd/fastmlx has no such mode; its tests fabricate one-element tensors
 generator keyed by (seed, tensor name), so they do not depend on the order in which
 tensors are made or on sharding: matrices, embeddings and biases N(0, 0.02), norm
 weights 1 + N(0, 0.02) (N(0, 0.1) where they are stored around zero), convolution taps
-N(0, 0.5), decay rates and their biases such that decays spread over (0, 1), drawn in 32-bit
+N(0, 0.5), the scalar of a dynamic tanh between 0.5 and 1.5, decay rates and their biases such that decays spread over (0, 1), drawn in 32-bit
 and then cast to the stored dtype.
 """
 from __future__ import annotations
@@ -37,6 +37,8 @@ def random_tensor(seed: int, name: str, shape, kind: str, dtype=torch.bfloat16, 
         t = torch.log(torch.sigmoid(t) * 0.98 + 0.02)
     elif kind == "rate_bias":
         t = t * 0.5 - 1.0
+    elif kind == "alpha":                   # the scalar of a dynamic tanh: between 0.5 and 1.5
+        t = torch.sigmoid(t) + 0.5
     elif kind == "norm0":                   # a norm weight stored around zero
         t = t * 0.1
     else:

@@ -169,3 +169,190 @@ def paged_attention_by_rows(q, kv, rows, block_tables, nh, nkv, hd, scale, windo
             out[at:at + ql, h * hd:(h + 1) * hd] = torch.softmax(s, dim=-1) @ V[:, h // rep, :]
         at += ql
     return out.to(q.dtype)
+
+
+# ----------------------------------------------------------------------------- general attention route, latents, experts
+def _rotate(heads, positions, inv_freq, rotary_dim, traditional):
+    if not rotary_dim:
+        return heads
+    ang = (positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]).to(F64)
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out, r = heads.clone(), rotary_dim
+    if traditional:
+        a, b = heads[..., 0:r:2], heads[..., 1:r:2]
+        out[..., 0:r:2] = a * cos - b * sin
+        out[..., 1:r:2] = b * cos + a * sin
+    else:
+        a, b = heads[..., :r // 2], heads[..., r // 2:r]
+        out[..., :r // 2] = a * cos - b * sin
+        out[..., r // 2:r] = b * cos + a * sin
+    return out
+
+
+def qk_prepare(qkv, positions, inv_freq, rotary_dim, traditional, norm_eps, slot_mapping, kv, nh, nkv, hd, vd, status,
+               bias=None, q_weight=None, k_weight=None, norm_first=False):
+    T = qkv.shape[0]
+    n_qk = (nh + nkv) * hd
+    row = qkv[:, :n_qk + nkv * vd].to(F64)
+    if bias is not None:
+        row = row + bias.to(F64)
+    heads = row[:, :n_qk].reshape(T, nh + nkv, hd)
+    w = torch.ones(nh + nkv, hd, dtype=F64)
+    if q_weight is not None:
+        w[:nh], w[nh:] = q_weight.to(F64), k_weight.to(F64)
+
+    def norm(h):
+        return h if norm_eps is None else h / torch.sqrt((h * h).mean(-1, keepdim=True) + norm_eps) * w
+
+    heads = _rotate(norm(heads), positions, inv_freq, rotary_dim, traditional) if norm_first \
+        else norm(_rotate(heads, positions, inv_freq, rotary_dim, traditional))
+    q = heads[:, :nh].reshape(T, nh * hd).to(torch.float32)
+    if kv is not None and slot_mapping is not None and nkv:
+        pages = kv.shape[0]
+        ps = kv[0].numel() // (nkv * (hd + vd))
+        flat = kv.view(pages, -1)
+        for t in range(T):
+            s = int(slot_mapping[t])
+            if s < 0:
+                continue
+            if s >= pages * ps:
+                status[0] = 2
+                continue
+            pg, off = s // ps, s % ps
+            for g in range(nkv):
+                flat[pg, (g * ps + off) * hd:(g * ps + off + 1) * hd] = heads[t, nh + g].to(kv.dtype)
+                at = nkv * ps * hd + (g * ps + off) * vd
+                flat[pg, at:at + vd] = row[t, n_qk + g * vd:n_qk + (g + 1) * vd].to(kv.dtype)
+    return q
+
+
+def paged_attention_general(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, window, page_size, out=None,
+                            keep_first=0, values_are_keys=False, gate=None):
+    T = q.shape[0]
+    pages = kv.shape[0]
+    flat = kv.reshape(pages, -1)
+    res = torch.zeros(T, nh * vd, dtype=F64)
+    rep = nh // nkv
+    width = hd if values_are_keys else hd + vd
+    for t in range(T):
+        pos = int(ctx.positions[t])
+        if pos < 0:
+            continue
+        bt = group.block_tables[int(ctx.token_row[t])]
+        lo = max(0, pos - window + 1) if window > 0 else 0
+        js = [j for j in range(pos + 1) if j >= lo or j < keep_first]
+        for h in range(nh):
+            g = h // rep
+            K, V = [], []
+            for j in js:
+                pg = int(bt[j // page_size])
+                if pg < 0:
+                    ctx.status[0] = 3
+                    pg = 0
+                at = (g * page_size + j % page_size)
+                K.append(flat[pg, at * hd:(at + 1) * hd])
+                V.append(K[-1] if values_are_keys else
+                         flat[pg, nkv * page_size * hd + at * vd: nkv * page_size * hd + (at + 1) * vd])
+            K, V = torch.stack(K).to(F64), torch.stack(V).to(F64)
+            s = (K @ q[t, h * hd:(h + 1) * hd].to(F64)) * scale
+            if softcap and softcap > 0:
+                s = softcap * torch.tanh(s / softcap)
+            res[t, h * vd:(h + 1) * vd] = torch.softmax(s, 0) @ V
+    if gate is not None:
+        res = res * torch.sigmoid(gate.to(F64))
+    res = res.to(kv.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def dyt_step(y, post, mult, add, residual, pre, out_dtype, out=None, keep_stream=True):
+    ref = y if y is not None else residual
+    s = residual.to(F64) if residual is not None else torch.zeros(ref.shape, dtype=F64)
+    if y is not None:
+        v = y.to(F64)
+        if post:
+            v = torch.tanh(post[0] * v) * post[1].to(F64) + post[2].to(F64)
+        s = s + mult * v
+    if add is not None:
+        s = s + add.to(F64)
+    if residual is None:
+        residual = s.to(torch.float32)
+    else:
+        residual.copy_(s.to(torch.float32))
+    if pre is False:
+        return None, residual
+    s = residual.to(F64)
+    o = (torch.tanh(pre[0] * s) * pre[1].to(F64) + pre[2].to(F64)) if pre else s
+    if out is not None:
+        out.copy_(o.to(out.dtype))
+        return out, residual
+    return o.to(out_dtype), residual
+
+
+def rmsnorm_rows(x, weight, eps, out=None, out_dtype=None, row_map=None, status=None):
+    h = x.to(F64)
+    y = h / torch.sqrt((h * h).mean(-1, keepdim=True) + eps) * weight.to(F64)
+    if row_map is None:
+        if out is None:
+            return y.to(out_dtype or x.dtype)
+        out.copy_(y.to(out.dtype))
+        return out
+    rows = out.view(-1, x.shape[1])
+    for t in range(x.shape[0]):
+        r = int(row_map[t])
+        if r < 0:
+            continue
+        if r >= rows.shape[0]:
+            status[0] = 2
+            continue
+        rows[r] = y[t].to(out.dtype)
+    return out
+
+
+def sigmoid_gate(o, gate, group=1):
+    g = torch.sigmoid(gate.to(F64)).repeat_interleave(group, dim=1)
+    o.copy_((o.to(F64) * g).to(o.dtype))
+    return o
+
+
+def moe_route(logits, top, groups=1, keep=1, want_chosen=False):
+    T, E = logits.shape
+    s = torch.softmax(logits.to(torch.float32), -1)
+    w = torch.zeros(T, E, dtype=torch.float32)
+    chosen = torch.full((T, top), -1, dtype=torch.int32)
+    for t in range(T):
+        ok = [True] * E
+        if groups > 1 and keep < groups:
+            per = E // groups
+            best = [max(float(s[t, e]) for e in range(g * per, (g + 1) * per)) for g in range(groups)]
+            kept = sorted(range(groups), key=lambda g: (-best[g], g))[:keep]
+            ok = [e // per in kept for e in range(E)]
+        order = sorted((e for e in range(E) if ok[e]), key=lambda e: (-float(s[t, e]), e))[:top]
+        for i, e in enumerate(order):
+            w[t, e] = s[t, e]
+            chosen[t, i] = e
+    return (w, chosen) if want_chosen else w
+
+
+def moe_expert_act(gu, weights, E, ff, limit, limit_shared=0.0, out=None):
+    T, F = gu.shape[0], gu.shape[1] // 2
+    g, u = gu[:, :F].to(F64), gu[:, F:].to(F64)
+    lim = torch.full((F,), float(limit), dtype=F64)
+    lim[E * ff:] = float(limit_shared)
+    w = torch.ones(T, F, dtype=F64)
+    w[:, :E * ff] = weights.to(F64).repeat_interleave(ff, dim=1)
+    g = torch.minimum(g, lim)
+    u = torch.maximum(torch.minimum(u, lim), -lim)
+    y = (w * g * torch.sigmoid(1.702 * g) * (u + 1)).to(gu.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def head_linear(x, w, out_dtype):
+    H, N, K = w.shape
+    T = x.shape[0]
+    return torch.einsum("thk,hnk->thn", x.reshape(T, H, K).to(F64), w.to(F64)).reshape(T, H * N).to(out_dtype)
