@@ -229,35 +229,34 @@ def qk_prepare(qkv, positions, inv_freq, rotary_dim, traditional, norm_eps, slot
 def paged_attention_general(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, window, page_size, out=None,
                             keep_first=0, values_are_keys=False, gate=None):
     T = q.shape[0]
-    pages = kv.shape[0]
-    flat = kv.reshape(pages, -1)
+    flat = kv.reshape(-1)
     res = torch.zeros(T, nh * vd, dtype=F64)
     rep = nh // nkv
-    width = hd if values_are_keys else hd + vd
+    page_elems = nkv * page_size * (hd if values_are_keys else hd + vd)
     for t in range(T):
         pos = int(ctx.positions[t])
         if pos < 0:
             continue
         bt = group.block_tables[int(ctx.token_row[t])]
         lo = max(0, pos - window + 1) if window > 0 else 0
-        js = [j for j in range(pos + 1) if j >= lo or j < keep_first]
-        for h in range(nh):
-            g = h // rep
-            K, V = [], []
-            for j in js:
-                pg = int(bt[j // page_size])
-                if pg < 0:
-                    ctx.status[0] = 3
-                    pg = 0
-                at = (g * page_size + j % page_size)
-                K.append(flat[pg, at * hd:(at + 1) * hd])
-                V.append(K[-1] if values_are_keys else
-                         flat[pg, nkv * page_size * hd + at * vd: nkv * page_size * hd + (at + 1) * vd])
-            K, V = torch.stack(K).to(F64), torch.stack(V).to(F64)
-            s = (K @ q[t, h * hd:(h + 1) * hd].to(F64)) * scale
-            if softcap and softcap > 0:
-                s = softcap * torch.tanh(s / softcap)
-            res[t, h * vd:(h + 1) * vd] = torch.softmax(s, 0) @ V
+        js = torch.tensor([j for j in range(pos + 1) if j >= lo or j < keep_first])
+        pages = bt[(js // page_size).long()].long()
+        if (pages < 0).any():
+            ctx.status[0] = 3
+            continue
+        for g in range(nkv):
+            at = pages * page_elems + (g * page_size + js % page_size) * hd
+            K = flat[at[:, None] + torch.arange(hd)[None, :]].to(F64)
+            if values_are_keys:
+                V = K
+            else:
+                at = pages * page_elems + nkv * page_size * hd + (g * page_size + js % page_size) * vd
+                V = flat[at[:, None] + torch.arange(vd)[None, :]].to(F64)
+            for h in range(g * rep, (g + 1) * rep):
+                s = (K @ q[t, h * hd:(h + 1) * hd].to(F64)) * scale
+                if softcap and softcap > 0:
+                    s = softcap * torch.tanh(s / softcap)
+                res[t, h * vd:(h + 1) * vd] = torch.softmax(s, 0) @ V
     if gate is not None:
         res = res * torch.sigmoid(gate.to(F64))
     res = res.to(kv.dtype)
