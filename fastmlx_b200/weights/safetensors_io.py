@@ -134,7 +134,7 @@ def write_file(path: str, tensors: dict[str, torch.Tensor], metadata: dict | Non
         for name in order:
             t = tensors[name].detach().contiguous().cpu()
             if t.numel():
-                f.write(memoryview(t.view(torch.uint8).reshape(-1).numpy()))       # no second copy of the bytes
+                f.write(memoryview(t.reshape(-1).view(torch.uint8).numpy()))       # no second copy of the bytes; a scalar too
     os.replace(tmp, path)
 
 
