@@ -29,6 +29,9 @@ timed; nothing reaches around the scheduler.  One JSON line is printed:
 3.1-8B (a few layers each), a Medirax model of equal width, heads and parameter count per layer (three gated
 delta rule layers to one layer of capped sliding-window attention, a dense feed-forward of squared relu) beside
 the Llama layers: a 2,048-token prompt whole and in portions of 512, and steady decoding at batch 8 and 64.
+`--design-set llama,medirax,gekavik` chooses the designs; a Gekavik model of those sizes has windowed attention that
+keeps the first tokens, latent attention in every fourth layer, and a mixture of 32 experts (4 per token and a shared
+one) whose active parameters equal the Llama layer's.
 
 Every timed step reads well over 126 MB (weights alone are 2.5 GB), so no input stays in L2
 between iterations.  tamnd/fastmlx publishes no number to compare with, and cannot run here
@@ -388,6 +391,42 @@ def medirax_like(shape: dict, layers: int, window: int = 1024) -> dict:
             "layers": [att if i % 4 == 3 else dl for i in range(layers)]}
 
 
+def gekavik_like(shape: dict, layers: int, window: int = 1024) -> dict:
+    """A Gekavik configuration with a Llama shape's width, heads and vocabulary: windowed attention that keeps the first
+    four tokens, every fourth layer (from the second on) latent attention with a cached latent of 256; a mixture of 32
+    experts in 8 groups (4 kept), 4 per token, each an eighth of the gated feed-forward's hidden size, and a shared
+    expert of half of it: the parameters a token uses equal the Llama layer's, the parameters held are 4.5 times as many.
+    The second and third layer form a loop of one pass, so that a loop's entry product is in the step."""
+    d, nh, nkv, hd = shape["hidden_size"], shape["num_attention_heads"], shape["num_key_value_heads"], shape["head_dim"]
+    ff = shape["intermediate_size"]
+    mlp = {"kind": "moe", "router": {"experts": 32, "top": 4, "groups": {"count": 8, "keep": 4}},
+           "expert": {"ff": ff // 8, "limit": 7.0}, "shared": {"ff": ff // 2, "limit": 7.0}}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                     "mask": {"size": window, "keep_first": 4}, "rot": {"dims": hd, "base": 10000.0}}}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": nh, "dim": hd, "vdim": hd, "q_rank": d // 2, "kv_rank": 256, "scale": hd ** -0.5,
+                     "mask": {"size": window}}}
+    cfg = {"architecture": "Gekavik", "vocab": shape["vocab_size"], "width": d, "residual_mult": 0.5, "norm": {"eps": 1e-6},
+           "layers": [lat if i % 4 == 1 else att for i in range(layers)]}
+    if layers >= 3:
+        cfg["loop"] = {"start": 1, "stop": 3, "times": 1}
+    return cfg
+
+
+def step_weight_bytes(model, tokens: int) -> int:
+    """Bytes of weights a step of `tokens` tokens must read: every run of the schedule reads its layer (a looped layer
+    once per pass); a routed feed-forward with grouped products reads the experts its tokens chose, at most."""
+    total = model.weight_bytes() - sum(layer.weight_bytes() for layer in model.layers)
+    for run in model.schedule:
+        layer = model.layers[run.layer]
+        total += layer.weight_bytes()
+        ffn = getattr(layer, "ffn", None)
+        if ffn is not None and hasattr(ffn, "active_weight_bytes"):
+            total -= ffn.weight_bytes() - ffn.active_weight_bytes(tokens)
+    return total
+
+
 def design_numbers(cfg: dict, vocab: int, pk: dict, context: int, steps: int, warmup: int) -> dict:
     """Prefill of 2,048 tokens (whole, in 512s) and steady decoding at batch 8 and 64 behind `context` tokens, through
     Engine.step(), for one configuration of either design."""
@@ -410,7 +449,7 @@ def design_numbers(cfg: dict, vocab: int, pk: dict, context: int, steps: int, wa
         steady_decode(engine, b, min(context, 512), 8, warmup, vocab, nums, False)              # graphs
         pt = steady_decode(engine, b, context, steps, warmup, vocab, nums, False)
         live = type("R", (), {"length": pt["ctx"]})
-        step_bytes = weight_bytes + b * (engine.manager.kv_bytes_read(live) + state_bytes)
+        step_bytes = step_weight_bytes(engine.model, b) + b * (engine.manager.kv_bytes_read(live) + state_bytes)
         out[f"decode_b{b}"] = {"ms_per_step": round(pt["ms"], 4), "tok_s": round(b / (pt["ms"] / 1e3), 1),
                                "gb_per_step": round(step_bytes / 1e9, 3),
                                "hbm_frac": round(step_bytes / (pt["ms"] / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
@@ -420,14 +459,15 @@ def design_numbers(cfg: dict, vocab: int, pk: dict, context: int, steps: int, wa
     return out
 
 
-def compare_designs(shapes, layers: int, context: int, steps: int, warmup: int, pk: dict) -> dict:
+def compare_designs(shapes, layers: int, context: int, steps: int, warmup: int, pk: dict, which=("llama", "medirax")) -> dict:
     out = {}
     for key in shapes:
         name, shape = SHAPES[key]
-        llama = dict(shape, num_hidden_layers=layers)
-        out[key] = {"layers": layers, "context": context,
-                    "llama": design_numbers(llama, shape["vocab_size"], pk, context, steps, warmup),
-                    "medirax": design_numbers(medirax_like(shape, layers), shape["vocab_size"], pk, context, steps, warmup)}
+        make = {"llama": lambda: dict(shape, num_hidden_layers=layers), "medirax": lambda: medirax_like(shape, layers),
+                "gekavik": lambda: gekavik_like(shape, layers)}
+        out[key] = {"layers": layers, "context": context}
+        for design in which:
+            out[key][design] = design_numbers(make[design](), shape["vocab_size"], pk, context, steps, warmup)
     return out
 
 
@@ -449,6 +489,8 @@ def main() -> int:
     ap.add_argument("--designs", default="", help="layer sizes (comma-separated, e.g. 1b,8b) at which a Medirax model and the Llama "
                     "layers of equal size are measured side by side; prints that comparison alone")
     ap.add_argument("--design-layers", type=int, default=8, help="layers of each model of the --designs comparison")
+    ap.add_argument("--design-set", default="llama,medirax", help="which designs the --designs comparison measures "
+                    "(comma-separated, of llama, medirax, gekavik)")
     ap.add_argument("--only-steps", type=int, default=0,
                     help="for a profiler's launch list: fill the batch, run this many decode steps and stop (no timing, no JSON line)")
     args = ap.parse_args()
@@ -472,9 +514,14 @@ def main() -> int:
     pk = peaks()
     if args.designs:
         keys = [k for k in args.designs.split(",") if k]
-        print(json.dumps({"compare": "medirax beside llama at equal layer sizes", "dtype": "bf16",
+        which = [w for w in args.design_set.split(",") if w]
+        if any(w not in ("llama", "medirax", "gekavik") for w in which):
+            print(f"bench.py: --design-set takes llama, medirax, gekavik (got {args.design_set!r})")
+            return 2
+        print(json.dumps({"compare": " beside ".join(which) + " at equal layer sizes", "dtype": "bf16",
                           "data": "synthetic: seeded uniform-random token ids, random weights", "peaks": pk["source"],
-                          "designs": compare_designs(keys, args.design_layers, min(args.context, 4096), min(steps, 64), warmup, pk)}))
+                          "designs": compare_designs(keys, args.design_layers, min(args.context, 4096), min(steps, 64), warmup, pk,
+                                                     which)}))
         return 0
     big = 64 if not args.no_points else args.batch
     pool_tokens = max(big, args.batch) * (args.context + 64) + PREFILL_TOKENS + 64

@@ -97,6 +97,7 @@ struct Cache {
   int nkv, page_size;
   long long num_pages;
   int page_shift;         // log2(page_size) when it is a power of two >= 4, else -1
+  int keys_only = 0;      // 1: a page holds keys alone, [nkv, page_size, HD], and they are the values too
 };
 
 __device__ __forceinline__ int page_shift_of(int page_size) {
@@ -109,8 +110,9 @@ __device__ __forceinline__ int page_shift_of(int page_size) {
 // read serves eight 16-byte copies.
 __device__ __forceinline__ void load_tiles(bf16* kdst, bf16* vdst, const Cache& c, int g, int k0, int kbeg, int kend,
                                            int* status, int where) {
-  const long long plane = (long long)c.nkv * c.page_size * HD;          // k plane -> v plane
-  const long long page_stride = 2 * plane;
+  const long long plane_k = (long long)c.nkv * c.page_size * HD;
+  const long long plane = c.keys_only ? 0 : plane_k;                    // k plane -> v plane
+  const long long page_stride = c.keys_only ? plane_k : 2 * plane_k;
   const bf16* base = c.kv + (long long)g * c.page_size * HD;
   if (c.page_shift >= 0 && k0 >= kbeg && k0 + BN <= kend) {
     // A tile inside the range (all but the first and last of a block): no key needs a test, and what does not
@@ -257,7 +259,7 @@ __device__ __forceinline__ void pv_tile(float (&o)[NT_O][4], const float (&p)[2 
 template <int NT, bool MASK, bool CAP = false>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&alpha)[2], float sl2,
                                              int key0, const int (&lim)[2], const int (&lo)[2], float cap_l2 = 0.f,
-                                             float scale_cap = 0.f) {
+                                             float scale_cap = 0.f, int keep = 0) {
   const int t = threadIdx.x & 3;
   float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -267,7 +269,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], f
       const int x = e >> 1;
       const int key = key0 + 8 * j + 2 * t + (e & 1);
       float v = -INFINITY;
-      if (!MASK || (key <= lim[x] && key >= lo[x])) {          // the cap is worked out for visible scores only
+      if (!MASK || (key <= lim[x] && (key >= lo[x] || key < keep))) {      // the cap is worked out for visible scores only
         if (CAP) v = cap_l2 * tanhf(s[j][e] * scale_cap);
         else v = s[j][e] * sl2;
       }
@@ -493,7 +495,7 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
                     const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ row_start,
                     const int* __restrict__ row_ctx, bf16* __restrict__ out, int nh, int nkv, int page_size,
                     long long num_pages, float scale, int window, int* status, float softcap, long long out_stride,
-                    const int* __restrict__ positions, float* split_out, int n_splits) {
+                    const int* __restrict__ positions, float* split_out, int n_splits, int keep_first, int keys_only) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   // The last query tiles of a row see the most keys.  Blocks start in the order x, y, z: with the
@@ -516,7 +518,8 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   const bool one_token = WIDE && q_len == 1 && rep <= 16;
   const int wrow = one_token ? 0 : warp * 16;      // the first packed row of this warp within the block's tile
   const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages,
-                page_shift_of(page_size)};
+                page_shift_of(page_size), WIDE ? keys_only : 0};
+  const int keep = WIDE && window > 0 ? keep_first : 0;      // a request's first tokens that stay visible behind the window
 
   // the two packed rows of this thread
   int prow[2], tok[2], head[2], lim[2], lo[2];
@@ -558,10 +561,13 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   // keys this block needs: from the first row's window start to the last row's position
   const int first_tok = prow0 / rep;
   const int last_tok = (min(prow0 + BM, n_packed) - 1) / rep;
-  const int kbeg = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
+  int kbeg = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
+  if ((kbeg & ~3) < keep) kbeg = 0;                   // the window's tiles would reach into the kept tokens: one run from 0
   const int kend = ctx + last_tok + 1;
   const int kstart = kbeg & ~3;                       // tiles start on a multiple of 4 keys
-  const int all_tiles = padding ? 0 : (kend - kstart + BN - 1) / BN;
+  // tiles of the kept first tokens come first, where the window has left them behind: keys [0, keep)
+  const int kept_tiles = (keep > 0 && kbeg > 0) ? (keep + BN - 1) / BN : 0;
+  const int all_tiles = padding ? 0 : kept_tiles + (kend - kstart + BN - 1) / BN;
   // this block's tiles: all of them, or its share of the row's
   const int per_split = shared_keys ? (all_tiles + n_splits - 1) / n_splits : all_tiles;
   const int tile0 = split * per_split;
@@ -583,18 +589,28 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
 
   auto stage_k = [&](int s) { return smem + (size_t)s * 2 * TILE; };
   auto stage_v = [&](int s) { return smem + (size_t)s * 2 * TILE + TILE; };
+  // tile i of the block: its first key, and the keys it may hold
+  auto tile_key = [&](int i) { return i < kept_tiles ? i * BN : kstart + (i - kept_tiles) * BN; };
+  auto fetch = [&](int stage, int i) {
+    if (i < kept_tiles) load_tiles(stage_k(stage), stage_v(stage), c, g, i * BN, 0, keep, status, r);
+    else load_tiles(stage_k(stage), stage_v(stage), c, g, tile_key(i), kbeg, kend, status, r);
+  };
+  // a tile of kept tokens shows keys below `keep` and nothing else
+  int lim_kept[2], lo_kept[2] = {0, 0};
+#pragma unroll
+  for (int x = 0; x < 2; ++x) lim_kept[x] = min(lim[x], keep - 1);
 #pragma unroll
   for (int s = 0; s < PREFILL_STAGES - 1; ++s) {
-    if (s < n_tiles) load_tiles(stage_k(s), stage_v(s), c, g, kstart + (tile0 + s) * BN, kbeg, kend, status, r);
+    if (s < n_tiles) fetch(s, tile0 + s);
     cp_async_commit();
   }
   for (int it = 0; it < n_tiles; ++it) {
     cp_async_wait<PREFILL_STAGES - 2>();
     __syncthreads();
     const int nx = it + PREFILL_STAGES - 1;
-    if (nx < n_tiles)
-      load_tiles(stage_k(nx % PREFILL_STAGES), stage_v(nx % PREFILL_STAGES), c, g, kstart + (tile0 + nx) * BN, kbeg, kend, status, r);
+    if (nx < n_tiles) fetch(nx % PREFILL_STAGES, tile0 + nx);
     cp_async_commit();
+    const bool kept_tile = tile0 + it < kept_tiles;
     const bf16* ks = stage_k(it % PREFILL_STAGES);
     const bf16* vs = stage_v(it % PREFILL_STAGES);
     if (WIDE && prow0 + wrow >= n_packed) continue;             // a warp without a row only copies
@@ -607,9 +623,12 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
         for (int e = 0; e < 4; ++e) s2[j][e] = 0.f;
       qk_tile<2, WIDE>(s2, qf, ks, 16 * warp, qf2);
       float alpha[2];
-      const int qk0 = kstart + (tile0 + it) * BN + 16 * warp;
-      if (capped) softmax_step<2, true, true>(s2, m, l, alpha, sl2, qk0, lim, lo, cap_l2, scale_cap);
-      else softmax_step<2, true>(s2, m, l, alpha, sl2, qk0, lim, lo);
+      const int qk0 = tile_key(tile0 + it) + 16 * warp;
+      if (kept_tile) {
+        if (capped) softmax_step<2, true, true>(s2, m, l, alpha, sl2, qk0, lim_kept, lo_kept, cap_l2, scale_cap);
+        else softmax_step<2, true>(s2, m, l, alpha, sl2, qk0, lim_kept, lo_kept);
+      } else if (capped) softmax_step<2, true, true>(s2, m, l, alpha, sl2, qk0, lim, lo, cap_l2, scale_cap, keep);
+      else softmax_step<2, true>(s2, m, l, alpha, sl2, qk0, lim, lo, 0.f, 0.f, keep);
 #pragma unroll
       for (int n = 0; n < NT_O; ++n) {
         o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
@@ -625,16 +644,20 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
       for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
     qk_tile<BN / 8, WIDE>(s, qf, ks, 0, qf2);
     float alpha[2];
-    const int tk0 = kstart + (tile0 + it) * BN;
-    const bool open = warp_full && tk0 >= sure_lo && tk0 + BN - 1 <= sure_hi;
-    if (capped && open)
+    const int tk0 = tile_key(tile0 + it);
+    const bool open = !kept_tile && warp_full && tk0 >= sure_lo && tk0 + BN - 1 <= sure_hi;
+    if (kept_tile && capped)
+      softmax_step<BN / 8, true, true>(s, m, l, alpha, sl2, tk0, lim_kept, lo_kept, cap_l2, scale_cap);
+    else if (kept_tile)
+      softmax_step<BN / 8, true>(s, m, l, alpha, sl2, tk0, lim_kept, lo_kept);
+    else if (capped && open)
       softmax_step<BN / 8, false, true>(s, m, l, alpha, sl2, tk0, lim, lo, cap_l2, scale_cap);
     else if (capped)
-      softmax_step<BN / 8, true, true>(s, m, l, alpha, sl2, tk0, lim, lo, cap_l2, scale_cap);
+      softmax_step<BN / 8, true, true>(s, m, l, alpha, sl2, tk0, lim, lo, cap_l2, scale_cap, keep);
     else if (open)
       softmax_step<BN / 8, false>(s, m, l, alpha, sl2, tk0, lim, lo);
     else
-      softmax_step<BN / 8, true>(s, m, l, alpha, sl2, tk0, lim, lo);
+      softmax_step<BN / 8, true>(s, m, l, alpha, sl2, tk0, lim, lo, 0.f, 0.f, keep);
 #pragma unroll
     for (int n = 0; n < NT_O; ++n) {
       o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
@@ -1253,7 +1276,7 @@ FMX_EXPORT int fmx_attn_prefill(const void* q, long long q_stride, const void* k
   dim3 grid(nkv, rows, (unsigned)tiles);
   attn_prefill_kernel<false><<<grid, THREADS, prefill_smem(), stream>>>(
       q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv,
-      page_size, num_pages, scale, window, status, 0.f, (long long)nh * HD, (const int*)nullptr, (float*)nullptr, 1);
+      page_size, num_pages, scale, window, status, 0.f, (long long)nh * HD, (const int*)nullptr, (float*)nullptr, 1, 0, 0);
   FMX_LAUNCH_CHECK();
   return 0;
 }
@@ -1261,13 +1284,16 @@ FMX_EXPORT int fmx_attn_prefill(const void* q, long long q_stride, const void* k
 // The form with 32-bit queries q[T, nh*hd] (row stride in floats), two-term products, capped scores (softcap > 0)
 // and an output whose rows are `out_stride` elements apart.  Takes every kind of row, single tokens included.
 // positions (or null): the step's token positions; a row whose first token stands at -1 is padding and gets zeros.
-FMX_EXPORT int fmx_attn_prefill_wide(const float* q, long long q_stride, const void* kv, const int* block_tables,
-                                     int bt_stride, const int* row_start, const int* row_ctx, const int* positions, void* out,
-                                     long long out_stride, int rows, int max_q_len, int nh, int nkv, int page_size,
-                                     long long num_pages, float scale, float softcap, int window, int* status,
-                                     float* scratch, long long scratch_floats, int n_splits, int n_tokens,
-                                     cudaStream_t stream) {
+// keep_first: beside a window, a request's first tokens that stay visible; keys_only: pages of keys [nkv, page, HD]
+// that are the values too.
+FMX_EXPORT int fmx_attn_prefill_wide_ex(const float* q, long long q_stride, const void* kv, const int* block_tables,
+                                        int bt_stride, const int* row_start, const int* row_ctx, const int* positions, void* out,
+                                        long long out_stride, int rows, int max_q_len, int nh, int nkv, int page_size,
+                                        long long num_pages, float scale, float softcap, int window, int* status,
+                                        float* scratch, long long scratch_floats, int n_splits, int n_tokens, int keep_first,
+                                        int keys_only, cudaStream_t stream) {
   if (rows == 0 || max_q_len == 0) return 0;
+  if (keep_first < 0) return fmx_fail("fmx_attn_prefill_wide: keep_first=%d", keep_first);
   if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0)
     return fmx_fail("fmx_attn_prefill_wide: bad sizes rows=%d nh=%d nkv=%d page=%d", rows, nh, nkv, page_size);
   if (rows > 65535 || nkv > 65535) return fmx_fail("fmx_attn_prefill_wide: too many rows or kv heads for one launch");
@@ -1293,16 +1319,27 @@ FMX_EXPORT int fmx_attn_prefill_wide(const float* q, long long q_stride, const v
     dim3 grid(nkv, rows, (unsigned)n_splits);
     attn_prefill_kernel<true><<<grid, THREADS, prefill_smem(), stream>>>(
         q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size,
-        num_pages, scale, window, status, softcap, out_stride, positions, scratch, n_splits);
+        num_pages, scale, window, status, softcap, out_stride, positions, scratch, n_splits, keep_first, keys_only);
     FMX_LAUNCH_CHECK();
     return 0;
   }
   dim3 grid(nkv, rows, (unsigned)tiles);
   attn_prefill_kernel<true><<<grid, THREADS, prefill_smem(), stream>>>(
       q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size,
-      num_pages, scale, window, status, softcap, out_stride, positions, (float*)nullptr, 1);
+      num_pages, scale, window, status, softcap, out_stride, positions, (float*)nullptr, 1, keep_first, keys_only);
   FMX_LAUNCH_CHECK();
   return 0;
+}
+
+FMX_EXPORT int fmx_attn_prefill_wide(const float* q, long long q_stride, const void* kv, const int* block_tables,
+                                     int bt_stride, const int* row_start, const int* row_ctx, const int* positions, void* out,
+                                     long long out_stride, int rows, int max_q_len, int nh, int nkv, int page_size,
+                                     long long num_pages, float scale, float softcap, int window, int* status,
+                                     float* scratch, long long scratch_floats, int n_splits, int n_tokens,
+                                     cudaStream_t stream) {
+  return fmx_attn_prefill_wide_ex(q, q_stride, kv, block_tables, bt_stride, row_start, row_ctx, positions, out, out_stride, rows,
+                                  max_q_len, nh, nkv, page_size, num_pages, scale, softcap, window, status, scratch,
+                                  scratch_floats, n_splits, n_tokens, 0, 0, stream);
 }
 
 // Second half of a launch with n_splits > 1: tokens [first_token, first_token + n_tokens) of the step.

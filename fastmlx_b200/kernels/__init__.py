@@ -391,43 +391,62 @@ def wide_attention_splits(rows: int, nkv: int, keys: int, device=None) -> int:
     return max(1, min(want, tiles // 2, WIDE_MAX_SPLITS))
 
 
-def _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, first_token: int = 0, splits: int = 1) -> None:
+def wide_attention_takes(q, kv, hd, vd, out=None) -> bool:
+    """`wide_attention_ok` for pages in either layout (keys and values, or keys that are the values too) and an
+    output that may be a slice of a wider buffer."""
+    return (kv is not None and kv.dtype == torch.bfloat16 and kv.dim() == 5 and q.dtype == torch.float32 and hd == vd
+            and hd % 16 == 0 and hd <= 256 and q.stride(0) % 2 == 0 and q.data_ptr() % 8 == 0
+            and (out is None or (out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)))
+
+
+def _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, first_token: int = 0, splits: int = 1,
+                 keep_first: int = 0) -> None:
     bt = group.block_tables
     scratch = None
     n_tokens = ctx.R
     if splits > 1:
         scratch = attention_scratch(q.device, (first_token + n_tokens) * nh * splits * (hd + 2))
-    call(f"attn_hd{hd}", "fmx_attn_prefill_wide", q.data_ptr(), q.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
+    call(f"attn_hd{hd}", "fmx_attn_prefill_wide_ex", q.data_ptr(), q.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
          ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), out.stride(0), ctx.R,
          int(ctx.max_q_len), nh, nkv, kv.shape[3], kv.shape[0], float(scale), float(softcap or 0.0), int(window),
          _ptr(ctx.status), _ptr(scratch), scratch.numel() if scratch is not None else 0, int(splits),
-         first_token + n_tokens, _stream())
+         first_token + n_tokens, int(keep_first), int(kv.shape[1] == 1), _stream())
     if splits > 1:
         call(f"attn_hd{hd}", "fmx_attn_wide_combine", scratch.data_ptr(), out.data_ptr(), out.stride(0), int(first_token),
              n_tokens, nh, int(splits), _stream())
 
 
-def paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out=None) -> torch.Tensor:
+def paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out=None, keep_first: int = 0,
+                         gate=None) -> torch.Tensor:
     """Attention of any mix of rows on the tensor cores with 32-bit scores and weights: the 32-bit queries
     q[T, nh*hd] and the probabilities enter the products as two bfloat16 terms each, sums are 32-bit, scores may be
     capped (softcap > 0).  `out` may be a slice of a wider buffer.  -> [T, nh*hd] in bfloat16.  The one-token rows
     (a whole decode step, or the rows at the head of a mixed step) have their keys shared out over several blocks
-    whose parts a second kernel puts together; the portions behind them take a launch of their own."""
+    whose parts a second kernel puts together; the portions behind them take a launch of their own.
+    `keep_first`: beside a window, a request's first tokens that stay visible; pages of shape [pages, 1, nkv, page, hd]
+    hold keys that are the values too; `gate` ([T, nh*hd]): the output is multiplied by sigmoid(gate) afterwards."""
+    out = _paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, int(keep_first))
+    if gate is not None:
+        sigmoid_gate(out, gate, 1)
+    return out
+
+
+def _paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, keep_first) -> torch.Tensor:
     T = q.shape[0]
     if out is None:
         out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=q.device)
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
     d = ctx.R if ctx.all_decode else getattr(ctx, "decode_rows", 0)
     if d <= 0:
-        _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out)
+        _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, keep_first=keep_first)
         return out
     longest = ctx.max_ctx_after if ctx.all_decode else ctx.decode_max_ctx
-    keys = min(window, longest) if window > 0 else longest
+    keys = min(window + keep_first, longest) if window > 0 else longest
     splits = wide_attention_splits(d, nkv, keys, q.device)
     if splits > 1 and d * nh * splits * (hd + 2) > ATTN_SCRATCH_FLOATS:
         splits = 1
     if ctx.all_decode:
-        _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, 0, splits)
+        _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, 0, splits, keep_first)
         return out
     key = ("wide attention rows", id(group))
     views = ctx.scratch.get(key)
@@ -435,8 +454,8 @@ def paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window,
         views = ctx.scratch[key] = (_rows_of(ctx, group, 0, d, 1, ctx.decode_max_ctx),
                                     _rows_of(ctx, group, d, ctx.R, ctx.rest_max_q_len, ctx.rest_max_ctx))
     (dctx, dgroup), (rctx, rgroup) = views
-    _wide_launch(q, kv, dctx, dgroup, nh, nkv, hd, scale, softcap, window, out, 0, splits)     # the one-token rows come first
-    _wide_launch(q, kv, rctx, rgroup, nh, nkv, hd, scale, softcap, window, out)
+    _wide_launch(q, kv, dctx, dgroup, nh, nkv, hd, scale, softcap, window, out, 0, splits, keep_first)     # the one-token rows come first
+    _wide_launch(q, kv, rctx, rgroup, nh, nkv, hd, scale, softcap, window, out, keep_first=keep_first)
     return out
 
 
@@ -567,6 +586,66 @@ def moe_expert_act(gu, weights, E: int, ff: int, limit: float, limit_shared: flo
         out = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
     call("common", "fmx_moe_expert_act", gu.data_ptr(), gu.stride(0), weights.data_ptr(), out.data_ptr(), out.stride(0), T,
          int(E), int(ff), F, float(limit), float(limit_shared), _dt(gu), _stream())
+    return out
+
+
+MOE_TILE_ROWS = 64
+
+
+def moe_sort(chosen, weights):
+    """The (token, chosen expert) pairs laid out expert by expert, each expert's pairs starting on a multiple of 64
+    rows.  chosen int32 [T, top] (-1: none), weights 32-bit [T, E].  -> a plan for the grouped products: (token of each
+    sorted row or -1, weight of each sorted row, sorted row of each pair, expert of each tile of 64 rows or -1, tiles)."""
+    _need_cuda(chosen, weights)
+    T, top = chosen.shape
+    E = weights.shape[1]
+    assert chosen.dtype == torch.int32 and chosen.is_contiguous() and weights.dtype == torch.float32 and weights.is_contiguous()
+    tiles = -(-(T * top + E * (MOE_TILE_ROWS - 1)) // MOE_TILE_ROWS)
+    dev = chosen.device
+    sorted_token = torch.empty(tiles * MOE_TILE_ROWS, dtype=torch.int32, device=dev)
+    sorted_w = torch.empty(tiles * MOE_TILE_ROWS, dtype=torch.float32, device=dev)
+    pair_pos = torch.empty(T * top, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev)
+    call("bf16", "fmx_moe_sort", chosen.data_ptr(), weights.data_ptr(), T, E, top, sorted_token.data_ptr(), sorted_w.data_ptr(),
+         pair_pos.data_ptr(), tile_expert.data_ptr(), tiles, _stream())
+    return sorted_token, sorted_w, pair_pos, tile_expert, tiles
+
+
+def moe_grouped_gate_up(x, plan, gate_up, E: int, ff: int, limit: float) -> torch.Tensor:
+    """The experts' hidden layers for the sorted pairs of `plan`: gate_up [2 E ff, K] bfloat16 holds every expert's gate
+    rows and then every expert's up rows; row r of the result is w g' sigmoid(1.702 g') (u' + 1) of the row's token under
+    the row's expert (clamped by `limit`, scaled by the pair's weight); padding rows are zero.  -> bfloat16 [tiles * 64, ff]."""
+    sorted_token, sorted_w, _, tile_expert, tiles = plan
+    _need_cuda(x, gate_up)
+    K = x.shape[1]
+    assert x.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16 and gate_up.is_contiguous() and x.stride(1) == 1
+    assert gate_up.shape == (2 * E * ff, K)
+    y = torch.empty((tiles * MOE_TILE_ROWS, ff), dtype=torch.bfloat16, device=x.device)
+    call("bf16", "fmx_moe_grouped_gate_up", x.data_ptr(), x.stride(0), sorted_token.data_ptr(), sorted_w.data_ptr(),
+         tile_expert.data_ptr(), gate_up.data_ptr(), gate_up.data_ptr() + 2 * E * ff * K, K, ff * K, y.data_ptr(), tiles, ff, K,
+         float(limit), _stream())
+    return y
+
+
+def moe_grouped_down(y, plan, down, E: int, ff: int) -> torch.Tensor:
+    """The pairs' outputs: down [d, E ff] bfloat16 holds the experts' down matrices side by side.  -> 32-bit [tiles * 64, d]."""
+    sorted_token, _, _, tile_expert, tiles = plan
+    d = down.shape[0]
+    assert down.dtype == torch.bfloat16 and down.is_contiguous() and down.shape[1] == E * ff and y.is_contiguous()
+    out = torch.empty((tiles * MOE_TILE_ROWS, d), dtype=torch.float32, device=y.device)
+    call("bf16", "fmx_moe_grouped_down", y.data_ptr(), sorted_token.data_ptr(), tile_expert.data_ptr(), down.data_ptr(), E * ff, ff,
+         out.data_ptr(), tiles, d, ff, _stream())
+    return out
+
+
+def moe_combine(pair_out, plan, shared, T: int, top: int, out_dtype) -> torch.Tensor:
+    """Each token's pair outputs added in the order of its choices, plus `shared` [T, d] where given; rounded once."""
+    pair_pos = plan[2]
+    d = pair_out.shape[1]
+    out = torch.empty((T, d), dtype=out_dtype, device=pair_out.device)
+    assert shared is None or (shared.dtype == out_dtype and shared.stride(1) == 1 and shared.shape == (T, d))
+    call("bf16", "fmx_moe_combine", pair_out.data_ptr(), pair_pos.data_ptr(), _ptr(shared), shared.stride(0) if shared is not None else 0,
+         _dt(out), out.data_ptr(), out.stride(0), _dt(out), T, d, int(top), _stream())
     return out
 
 

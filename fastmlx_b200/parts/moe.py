@@ -16,13 +16,20 @@ class RoutedExperts(FeedForward):
     Expert (no biases): g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit), W_down (g sigmoid(1.702 g) (u + 1)).
     The shared expert has the same form with a width and a limit of its own and weight 1.
 
-    All experts' gate and up matrices are stacked into one matrix and their down matrices laid side by side.  A step
-    runs the stacked product for every token, the activation kernel zeroes the columns of experts a token did not
-    choose and scales the others by the token's weight, and one product with the down matrices gives the weighted
-    sum, added up inside the product's 32-bit accumulators.  No token's result depends on what else is in the
-    batch, nothing loops on the host, and a decode step can be captured.  It reads every expert's weights and
-    multiplies experts / top times more than needed, which is the right trade for experts as small as a tile of
-    the product and the wrong one for large ones.
+    Two ways to compute it, chosen once by size (`sparse`), neither of which loops on the host or makes a token's
+    result depend on what else is in the batch, so that a decode step can be captured:
+
+    * all experts side by side (small experts, and the 32-bit path): all gate and up matrices are stacked into one
+      matrix and the down matrices laid side by side; a step runs the stacked product for every token, the activation
+      kernel zeroes the columns of experts a token did not choose and scales the others by the token's weight, and one
+      product with the down matrices gives the weighted sum inside the product's 32-bit accumulators.  It reads every
+      expert's weights and multiplies experts / top times more than needed: right for experts as small as a tile of
+      the product, wrong for large ones.
+    * grouped products (bfloat16, large experts): the (token, expert) pairs are sorted expert by expert on the device,
+      a tiled kernel multiplies each tile of pairs with its expert's gate and up rows and applies the activation and
+      the pair's weight in its epilogue, a second one multiplies with the expert's down matrix, and a last kernel adds
+      a token's pair outputs in the order of its choices to the shared expert's output, in 32-bit.  Only chosen experts'
+      weights are read.
 
     Tensors, under `name`: router; e<i>.gate, e<i>.up, e<i>.down; shared.gate, shared.up, shared.down."""
 
@@ -31,7 +38,9 @@ class RoutedExperts(FeedForward):
     def __init__(self, width: int, experts: int, top: int, ff: int, limit: float, name: str, groups: int = 1,
                  keep: int = 1, shared_ff: int = 0, shared_limit: float = 0.0, weight_suffix: str = "",
                  expert_prefix: str = "e", shared_name: str = "shared", router_name: str = "router",
-                 proj_names=("gate", "up", "down")):
+                 proj_names=("gate", "up", "down"), sparse: bool | None = None):
+        """`sparse`: grouped products (True), all experts side by side (False), or by size (None): grouped where the
+        experts' matrices together pass SPARSE_MIN_BYTES and more than twice as many experts exist as a token uses."""
         self.width, self.E, self.top, self.ff, self.limit = int(width), int(experts), int(top), int(ff), float(limit)
         self.groups, self.keep = max(1, int(groups)), max(1, int(keep))
         if self.E % self.groups or not 0 < self.top <= self.E:
@@ -47,6 +56,8 @@ class RoutedExperts(FeedForward):
         self.up_names = [(f"{p}.{u}{weight_suffix}", w) for p, w in zip(pre, widths)]
         self.down_names = [(f"{p}.{d}{weight_suffix}", w) for p, w in zip(pre, widths)]
         self.router_name = f"{name}.{router_name}{weight_suffix}"
+        self.want_sparse = sparse
+        self.sparse = False
 
     def own_weight_specs(self):
         specs = [WeightSpec(self.router_name, (self.E, self.width), "matrix")]
@@ -54,13 +65,37 @@ class RoutedExperts(FeedForward):
         specs += [WeightSpec(n, (self.width, w), "matrix") for n, w in self.down_names]
         return specs
 
+    SPARSE_MIN_BYTES = 8 << 20
+
     def bind_own(self, tensors, rt: Runtime):
         self.router = to_compute(tensors[self.router_name], rt)
-        self.gate_up = torch.cat([to_compute(tensors[n], rt) for n, _ in self.gate_names + self.up_names], 0).contiguous()
-        self.down = torch.cat([to_compute(tensors[n], rt) for n, _ in self.down_names], 1).contiguous()
+        mats = [to_compute(tensors[n], rt) for n, _ in self.gate_names + self.up_names + self.down_names]
+        can = (rt.dtype == torch.bfloat16 and all(m.dtype == torch.bfloat16 for m in mats) and self.width % 8 == 0
+               and self.ff % 8 == 0 and rt.device.type == "cuda" and hasattr(rt.k, "moe_sort"))
+        big = 3 * self.E * self.ff * self.width * 2 >= self.SPARSE_MIN_BYTES and self.E > 2 * self.top
+        self.sparse = can and (big if self.want_sparse is None else bool(self.want_sparse))
+        n = len(self.gate_names)
+        gates, ups, downs = mats[:n], mats[n:2 * n], mats[2 * n:]
+        self.shared_gate_up = self.shared_down = None
+        if self.sparse and self.shared_ff:        # the shared expert is an ordinary gated feed-forward beside the routed ones
+            self.shared_gate_up = torch.cat([gates.pop(), ups.pop()], 0).contiguous()
+            self.shared_down = downs.pop().contiguous()
+        self.gate_up = torch.cat(gates + ups, 0).contiguous()
+        self.down = torch.cat(downs, 1).contiguous()
 
     def weight_bytes(self):
-        return sum(t.numel() * t.element_size() for t in (self.router, self.gate_up, self.down))
+        """Bytes a step reads when every expert is used (a decode step of a few tokens reads fewer with grouped products)."""
+        return sum(t.numel() * t.element_size() for t in (self.router, self.gate_up, self.down, self.shared_gate_up,
+                                                           self.shared_down) if t is not None)
+
+    def active_weight_bytes(self, tokens: int) -> int:
+        """Bytes of weights a step of `tokens` tokens reads at most: all with the experts side by side; with grouped
+        products the router, the shared expert and at most tokens * top experts."""
+        if not self.sparse:
+            return self.weight_bytes()
+        e = self.router.element_size()
+        used = min(self.E, tokens * self.top)
+        return e * (self.router.numel() + 3 * used * self.ff * self.width + 3 * self.shared_ff * self.width)
 
     def route(self, x):
         """-> the tokens' weights over the experts, 32-bit [T, E], zero where an expert is not chosen."""
@@ -69,7 +104,22 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x, ctx):
         k = self.rt.k
+        if self.sparse:
+            return self.forward_grouped(x)
         w = self.route(x)
         gu = k.linear(x, self.gate_up, None, self.rt.dtype)
         act = k.moe_expert_act(gu, w, self.E, self.ff, self.limit, self.shared_limit)
         return k.linear(act, self.down, None, self.rt.dtype)
+
+    def forward_grouped(self, x):
+        k, T = self.rt.k, x.shape[0]
+        w, chosen = k.moe_route(k.linear(x, self.router, None, torch.float32), self.top, self.groups, self.keep, want_chosen=True)
+        plan = k.moe_sort(chosen, w)
+        y = k.moe_grouped_gate_up(x, plan, self.gate_up, self.E, self.ff, self.limit)
+        pairs = k.moe_grouped_down(y, plan, self.down, self.E, self.ff)
+        shared = None
+        if self.shared_gate_up is not None:
+            gu = k.linear(x, self.shared_gate_up, None, self.rt.dtype)
+            none = torch.empty((T, 0), dtype=torch.float32, device=x.device)
+            shared = k.linear(k.moe_expert_act(gu, none, 0, 1, 0.0, self.shared_limit), self.shared_down, None, self.rt.dtype)
+        return k.moe_combine(pairs, plan, shared, T, self.top, self.rt.dtype)

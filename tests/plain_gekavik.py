@@ -103,29 +103,39 @@ def expert(h, gate, up, down, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1)) @ down.T
 
 
-def route(z, top, groups, keep):
+def route(z, top, groups, keep, margins=None):
     """z [T, E] router logits -> weights [T, E], zero where an expert is not chosen: softmax scores; a group
-    of neighbouring experts scores as its best member; only the `keep` best groups may be chosen from."""
+    of neighbouring experts scores as its best member; only the `keep` best groups may be chosen from.
+    `margins`, a list, receives [T]: by how much (in logits) each token's choice is decided, the smaller of the
+    gap between the last kept group and the first that is not, and between the last chosen expert and the next."""
     T, E = z.shape
     s = torch.softmax(z, -1)
     allowed = torch.ones_like(s, dtype=torch.bool)
+    gap = torch.full((T,), math.inf, dtype=z.dtype)
     if groups and groups > 1 and keep < groups:
         per = E // groups
         best = s.view(T, groups, per).max(-1).values
         kept = torch.zeros(T, groups, dtype=torch.bool)
         kept.scatter_(1, best.topk(keep, dim=-1).indices, True)
         allowed = kept[:, :, None].expand(T, groups, per).reshape(T, E)
+        zb = z.view(T, groups, per).max(-1).values.sort(-1, descending=True).values
+        gap = zb[:, keep - 1] - zb[:, keep]
+    if margins is not None:
+        zs = z.masked_fill(~allowed, -math.inf).sort(-1, descending=True).values
+        if top < E:
+            gap = torch.minimum(gap, zs[:, top - 1] - zs[:, top])
+        margins.append(gap)
     chosen = s.masked_fill(~allowed, -1.0).topk(top, dim=-1).indices
     w = torch.zeros_like(s)
     w.scatter_(1, chosen, s.gather(1, chosen))
     return w
 
 
-def moe_ff(h, W, mlp, router_dtype=None):
+def moe_ff(h, W, mlp, margins=None):
     r = mlp["router"]
-    z = (h.to(router_dtype) @ W["router"].to(router_dtype).T).to(h.dtype) if router_dtype else h @ W["router"].T
+    z = h @ W["router"].T
     g = r.get("groups") or {}
-    w = route(z, r["top"], g.get("count", 1), g.get("keep", 1))
+    w = route(z, r["top"], g.get("count", 1), g.get("keep", 1), margins)
     out = torch.zeros_like(h)
     for e in range(r["experts"]):
         rows = torch.nonzero(w[:, e] > 0).flatten()
@@ -158,9 +168,9 @@ def layer_passes(config):
     return order + [(i, None) for i in range(b, n)]
 
 
-def forward(config, tensors, tokens, dtype=torch.float64, streams=None):
+def forward(config, tensors, tokens, dtype=torch.float64, streams=None, margins=None):
     """Logits [T, vocab] of one whole sequence; `streams`, a list, receives the residual stream after
-    every layer run."""
+    every layer run; `margins`, a list, every router's margins (see `route`)."""
     eps, r = config["norm"]["eps"], config["residual_mult"]
     emb = tensors["embed"].to(dtype)[torch.as_tensor(tokens, dtype=torch.long)]
     x = emb
@@ -174,7 +184,7 @@ def forward(config, tensors, tokens, dtype=torch.float64, streams=None):
         x = x + r * dynamic_tanh(y, *norm_of(tensors, f"l{i}.norm1b", dtype))
         if spec.get("mlp"):
             y = moe_ff(dynamic_tanh(x, *norm_of(tensors, f"l{i}.norm2", dtype)), sub(tensors, f"l{i}.mlp.", dtype),
-                       spec["mlp"])
+                       spec["mlp"], margins)
             x = x + r * dynamic_tanh(y, *norm_of(tensors, f"l{i}.norm2b", dtype))
         if streams is not None:
             streams.append(x.clone())

@@ -26,6 +26,10 @@ CASES = {
     "G4": dict(lens=[4, 40, 23, 66, 35, 80], page=16, max_tokens=256),
 }
 DEV = "cuda"
+# A router that takes bfloat16 inputs sees its logits moved by a few hundredths; where the plain model's own choice
+# of experts is decided by less (in some layer), either choice is right, and the position is not compared in bfloat16.
+CLOSE_CALL = 0.15
+CLOSE = {}
 
 
 def _prompts(name):
@@ -40,7 +44,12 @@ def models(tmp_path_factory):
         d = tg.make_model_dir(root, cfg, seed=23)
         W = tiny.load_plain_weights(d)
         prompts = _prompts(name)
-        out[name] = (d, W, prompts, {r: pg.forward(cfg, W, t) for r, t in prompts.items()})
+        ref = {}
+        for r, t in prompts.items():
+            margins = []
+            ref[r] = pg.forward(cfg, W, t, margins=margins)
+            CLOSE[(name, r)] = torch.stack(margins).min(0).values < CLOSE_CALL
+        out[name] = (d, W, prompts, ref)
     return out
 
 
@@ -55,12 +64,15 @@ def _run(model_dir, dtype, steps, max_tokens, page, max_live=4):
     return outs, rp
 
 
-def _compare(steps, outs, prompts, ref, tol):
+def _compare(steps, outs, prompts, ref, tol, skip=None):
     rows = traces.collect(steps, outs)
     for rid, toks in prompts.items():
         assert sorted(rows[rid]) == list(range(len(toks)))
         got = torch.from_numpy(np.stack([rows[rid][i] for i in range(len(toks))])).double()
         err = (got - ref[rid]).abs().max(dim=1).values / ref[rid].abs().max().item()
+        if skip is not None:
+            assert skip[rid].double().mean().item() < 0.5 or len(toks) < 8, "too few positions are compared"
+            err = err.masked_fill(skip[rid], 0.0)
         bad = torch.nonzero(err > tol)
         assert bad.numel() == 0, (f"request {rid}: first wrong position {int(bad[0])} of {len(toks)}, "
                                   f"error {err[int(bad[0])].item():.3e} (allowed {tol:.1e})")
@@ -78,7 +90,7 @@ def test_replay(models, name, dtype, cut):
     case = CASES[name]
     steps = CUTS[cut](prompts)
     outs, rp = _run(d, dtype, steps, case["max_tokens"], case["page"])
-    _compare(steps, outs, prompts, ref, TOL[dtype])
+    _compare(steps, outs, prompts, ref, TOL[dtype], {r: CLOSE[(name, r)] for r in prompts} if dtype == "bfloat16" else None)
     if cut == "mixed":
         need = sum(-(-len(t) // case["page"]) for t in prompts.values())
         assert all(need > g.pool.num_pages for g in rp.manager.groups), "the pool is too large for pages to be used again"
@@ -108,7 +120,7 @@ def test_long_decoding_moves_the_windows_over_decoded_tokens(models, dtype):
     sub = {"r3": prompts["r3"]}
     steps = traces.tail_decoded(sub, tail=130)
     outs, _ = _run(d, dtype, steps, 256, 16)
-    _compare(steps, outs, sub, ref, TOL[dtype])
+    _compare(steps, outs, sub, ref, TOL[dtype], {"r3": CLOSE[("G2", "r3")]} if dtype == "bfloat16" else None)
 
 
 # ----------------------------------------------------------------------------- kernels alone
@@ -189,8 +201,9 @@ def test_router_against_the_plain_choice(E, top, groups, keep):
     assert torch.equal(got.cpu() > 0, want > 0) and torch.allclose(got.cpu(), want, atol=1e-6)
     assert torch.equal(ids.cpu(), want_ids)
     assert torch.equal(k.moe_route(z.to(DEV), top, groups, keep).cpu(), got.cpu())
-    # the plain model's router, written independently, chooses the same
-    assert torch.equal(pg.route(z.double(), top, groups, keep) > 0, want > 0)
+    # the plain model's router, written independently, chooses the same (but for the row of ties, which it may break otherwise)
+    rows = [t for t in range(70) if t != 3]
+    assert torch.equal((pg.route(z.double(), top, groups, keep) > 0)[rows], (want > 0)[rows])
 
 
 def test_router_keeps_to_the_best_groups_where_a_better_expert_lies_outside():
@@ -226,6 +239,41 @@ def test_expert_activation_and_products_per_head(dtype):
         assert torch.allclose(got.cpu().double(), want, atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("E,top,ff,groups,keep,shared", [(8, 2, 24, 4, 2, 40), (6, 3, 64, 1, 1, 0), (16, 4, 8, 8, 3, 8), (3, 1, 136, 1, 1, 16)])
+@pytest.mark.parametrize("T", [1, 5, 70, 333])
+def test_grouped_products_of_the_routed_experts(E, top, ff, groups, keep, shared, T):
+    """The path of large experts on small ones: pairs sorted expert by expert on the device, tiles of 64 pairs against
+    their expert's matrices, outputs added per token; against the plain feed-forward and against the path that runs
+    all experts side by side."""
+    from fastmlx_b200.engine.loading import make_runtime
+    from fastmlx_b200.parts import RoutedExperts
+    d = 72
+    rt = make_runtime("bfloat16")
+    g = torch.Generator().manual_seed(E * 100 + T)
+    mlp = {"router": {"experts": E, "top": top, "groups": {"count": groups, "keep": keep}}, "expert": {"ff": ff, "limit": 0.9},
+           "shared": {"ff": shared, "limit": 1.7} if shared else None}
+    parts = {}
+    for sparse in (True, False):
+        parts[sparse] = RoutedExperts(d, E, top, ff, 0.9, "m", groups=groups, keep=keep, shared_ff=shared, shared_limit=1.7,
+                                      sparse=sparse)
+    W = {}
+    for spec in parts[True].weight_specs():
+        t = torch.randn(spec.shape, generator=g) / spec.shape[-1] ** 0.5
+        W[spec.name] = (t * (12.0 if spec.name.endswith("router") else 1.5)).bfloat16()
+    for p in parts.values():
+        p.bind(W, rt)
+    assert parts[True].sparse and not parts[False].sparse
+    x = torch.randn(T, d + 8, generator=g).bfloat16()
+    margins = []
+    want = pg.moe_ff(x[:, :d].double(), {n[2:]: t.double() for n, t in W.items()}, mlp, margins)
+    sure = margins[0] > CLOSE_CALL
+    got = {s: p.forward(x.to(DEV)[:, :d], None).cpu().double() for s, p in parts.items()}
+    scale = want.abs().max().item()
+    assert ((got[True] - want).abs().max(1).values[sure] < 2e-2 * scale).all()
+    assert ((got[True] - got[False]).abs().max(1).values[sure] < 1.5e-2 * scale).all()
+    assert sure.double().mean().item() > 0.5 or T < 8
+
+
 def _ctx(manager, reqs, lens, status):
     from fastmlx_b200.engine.batch import StepEntry, build_context
     entries = [StepEntry(r, [0] * n, []) for r, n in zip(reqs, lens)]
@@ -235,11 +283,12 @@ def _ctx(manager, reqs, lens, status):
 
 
 def _attention_case(window, keep, lens_by_step, standout, hd=16, vd=24, nh=4, nkv=2, page=16, dtype=torch.float32, rot=0,
-                    latent=False, gated=True, eps=1e-5):
+                    latent=False, gated=True, eps=1e-5, wide=False):
     """Requests fed in the given portions through the cache manager, `qk_prepare` (biases, q/k norm with a weight in
     front of an interleaved rotation) and the attention kernel; the query at position p of request 0 is aligned with
     the key at `standout(p)` so strongly that, where that key is seen, the output is its value.  `latent`: one kv
     head whose keys are the values too, written by `rmsnorm_rows` through the slot map.
+    `wide`: the tiled tensor-core kernel with two-term products instead of the one-warp-per-query kernel.
     -> (outputs per request, plain outputs, the values)."""
     from fastmlx_b200 import kernels as k
     from fastmlx_b200.cache.manager import CacheManager
@@ -306,13 +355,25 @@ def _attention_case(window, keep, lens_by_step, standout, hd=16, vd=24, nh=4, nk
         if latent:
             k.rmsnorm_rows(part[1].to(dev), kw.to(dev), eps, out=kv, row_map=grp.slot_mapping, status=status)
             q32 = part[0].to(dev).contiguous()
-            out = k.paged_attention_general(q32, kv, ctx, grp, nh, 1, hd, hd, scale, 0.0, window, page, values_are_keys=True)
+            if wide:
+                assert k.wide_attention_takes(q32, kv, hd, hd)
+                out = k.paged_attention_wide(q32, kv, ctx, grp, nh, 1, hd, scale, 0.0, window)
+            else:
+                out = k.paged_attention_general(q32, kv, ctx, grp, nh, 1, hd, hd, scale, 0.0, window, page, values_are_keys=True)
         else:
             qkv = torch.cat(part[:3], 1).to(dev).contiguous()         # 32-bit, as the product leaves it
             q32 = k.qk_prepare(qkv, ctx.positions, inv_freq, rot, True, eps, grp.slot_mapping, kv, nh, nkv, hd, vd, status,
                                bias=bias.to(dev), q_weight=qw.to(dev), k_weight=kw.to(dev), norm_first=True)
-            out = k.paged_attention_general(q32, kv, ctx, grp, nh, nkv, hd, vd, scale, 0.0, window, page, keep_first=spec.keep_first,
-                                            gate=part[3].to(dev).contiguous() if gated else None)
+            gate = part[3].to(dev).contiguous() if gated else None
+            if wide:
+                joined = torch.zeros((q32.shape[0], nh * vd + 6), dtype=dtype, device=dev)
+                assert k.wide_attention_takes(q32, kv, hd, vd, joined[:, 2:2 + nh * vd])
+                out = k.paged_attention_wide(q32, kv, ctx, grp, nh, nkv, hd, scale, 0.0, window, out=joined[:, 2:2 + nh * vd],
+                                             keep_first=spec.keep_first, gate=gate)
+                assert joined[:, :2].abs().max().item() == 0 and joined[:, 2 + nh * vd:].abs().max().item() == 0
+            else:
+                out = k.paged_attention_general(q32, kv, ctx, grp, nh, nkv, hd, vd, scale, 0.0, window, page,
+                                                keep_first=spec.keep_first, gate=gate)
         out = out.cpu().double()
         off = 0
         for r, n in live:
@@ -325,40 +386,43 @@ def _attention_case(window, keep, lens_by_step, standout, hd=16, vd=24, nh=4, nk
     return [torch.cat(x) for x in got], want, seqs
 
 
+KERNELS = [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)]
+KERNEL_IDS = ["float32", "bfloat16", "bfloat16-tiled"]
 HOW = {"prompt": [[150, 40]], "portions": [[31, 3], [2, 1], [37, 30], [38, 2], [42, 4]], "decoded": [[60, 1]] + [[1, 0]] * 90}
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,wide", KERNELS, ids=KERNEL_IDS)
 @pytest.mark.parametrize("edge", ["inside", "outside"])
 @pytest.mark.parametrize("how", ["prompt", "portions", "decoded"])
 @pytest.mark.parametrize("latent", [False, True])
-def test_attention_window_edge(dtype, edge, how, latent):
+def test_attention_window_edge(dtype, wide, edge, how, latent):
     """The key that stands out sits on the last place the window still holds, or one before it: its value must be the
     output, or must not be in it.  Pages that the window has passed are given back on the way."""
     window = 37
     standout = (lambda p: p - window + 1) if edge == "inside" else (lambda p: p - window)
-    got, want, _ = _attention_case(window, 3, HOW[how], standout, dtype=dtype, rot=8, latent=latent, gated=False)
+    kw = dict(dtype=dtype, rot=8, latent=latent, gated=False, wide=wide, vd=16 if wide else 24)
+    got, want, _ = _attention_case(window, 3, HOW[how], standout, **kw)
     tol = 2e-5 if dtype == torch.float32 else 3e-2
     for r in range(2):
         n_r = got[r].shape[0]
         assert torch.allclose(got[r], want[r][:n_r], atol=tol, rtol=tol), r
     # the oracle itself shows the edge: the outputs of the two cases differ where the key is seen
-    other, _, _ = _attention_case(window, 3, HOW[how], (lambda p: p - window) if edge == "inside" else (lambda p: p - window + 1),
-                                  dtype=dtype, rot=8, latent=latent, gated=False)
+    other, _, _ = _attention_case(window, 3, HOW[how], (lambda p: p - window) if edge == "inside" else (lambda p: p - window + 1), **kw)
     assert (got[0][100] - other[0][100]).abs().max().item() > 0.1
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,wide", KERNELS, ids=KERNEL_IDS)
 @pytest.mark.parametrize("edge", ["inside", "outside"])
 @pytest.mark.parametrize("how", ["prompt", "portions", "decoded"])
-@pytest.mark.parametrize("keep,page", [(3, 16), (19, 16), (1, 8), (16, 16)])
-def test_attention_kept_first_tokens(dtype, edge, how, keep, page):
+@pytest.mark.parametrize("keep,page", [(3, 16), (19, 16), (1, 8), (16, 16), (70, 16)])
+def test_attention_kept_first_tokens(dtype, wide, edge, how, keep, page):
     """The key that stands out is the last kept token, or the first that is not kept (seen only while the window
     still holds it): kept tokens are seen from far away, at their true positions, through pages that are never given
     back; the token after them is not."""
     window = 37
     j = keep - 1 if edge == "inside" else keep
-    got, want, seqs = _attention_case(window, keep, HOW[how], lambda p: j, dtype=dtype, rot=4, page=page)
+    got, want, seqs = _attention_case(window, keep, HOW[how], lambda p: j, dtype=dtype, rot=4, page=page, wide=wide,
+                                      vd=16 if wide else 24)
     tol = 2e-5 if dtype == torch.float32 else 3e-2
     for r in range(2):
         n_r = got[r].shape[0]
@@ -370,13 +434,13 @@ def test_attention_kept_first_tokens(dtype, edge, how, keep, page):
     assert ((far - value).abs().max().item() < 0.1) == (edge == "inside")
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,wide", KERNELS, ids=KERNEL_IDS)
 @pytest.mark.parametrize("latent", [False, True])
-def test_attention_far_key_among_hundreds(dtype, latent):
+def test_attention_far_key_among_hundreds(dtype, wide, latent):
     """No window: every query's key that stands out is position 1 (far back for late queries, among the first tokens
     for early ones); three requests of unequal length, page borders, values narrower than keys."""
-    got, want, _ = _attention_case(0, 0, [[330, 5, 64], [1, 1, 64], [2, 0, 1], [64, 16, 0]], lambda p: 1, hd=32, vd=8, nh=2, nkv=1,
-                                   dtype=dtype, rot=32, latent=latent)
+    got, want, _ = _attention_case(0, 0, [[330, 5, 64], [1, 1, 64], [2, 0, 1], [64, 16, 0]], lambda p: 1, hd=32, vd=32 if wide else 8, nh=2,
+                                   nkv=1, dtype=dtype, rot=32, latent=latent, wide=wide)
     tol = 2e-5 if dtype == torch.float32 else 3e-2
     for r in range(3):
         assert torch.allclose(got[r], want[r], atol=tol, rtol=tol), r
