@@ -297,7 +297,7 @@ def _attention_case(window, keep, lens_by_step, standout, hd=16, vd=24, nh=4, nk
     dev = torch.device(DEV)
     g = torch.Generator().manual_seed(window * 7 + hd + keep)
     if latent:
-        nkv, vd, rot, gated = 1, hd, 0, False
+        nkv, vd, rot, gated, keep = 1, hd, 0, False, 0
     totals = [sum(x) for x in zip(*lens_by_step)]
     qw, kw = 1 + 0.3 * torch.randn(hd, generator=g), 1 + 0.3 * torch.randn(hd, generator=g)
     bias = 0.1 * torch.randn((nh + nkv) * hd + nkv * vd, generator=g)
