@@ -400,7 +400,7 @@ def test_attention_window_edge(dtype, wide, edge, how, latent):
     output, or must not be in it.  Pages that the window has passed are given back on the way."""
     window = 37
     standout = (lambda p: p - window + 1) if edge == "inside" else (lambda p: p - window)
-    kw = dict(dtype=dtype, rot=8, latent=latent, gated=False, wide=wide, vd=16 if wide else 24)
+    kw = dict(dtype=dtype, rot=8, latent=latent, gated=False, wide=wide, hd=64, vd=64 if wide else 24)
     got, want, _ = _attention_case(window, 3, HOW[how], standout, **kw)
     tol = 2e-5 if dtype == torch.float32 else 3e-2
     for r in range(2):
@@ -421,8 +421,8 @@ def test_attention_kept_first_tokens(dtype, wide, edge, how, keep, page):
     back; the token after them is not."""
     window = 37
     j = keep - 1 if edge == "inside" else keep
-    got, want, seqs = _attention_case(window, keep, HOW[how], lambda p: j, dtype=dtype, rot=4, page=page, wide=wide,
-                                      vd=16 if wide else 24)
+    got, want, seqs = _attention_case(window, keep, HOW[how], lambda p: j, dtype=dtype, rot=4, page=page, wide=wide, hd=64,
+                                      vd=64 if wide else 24)
     tol = 2e-5 if dtype == torch.float32 else 3e-2
     for r in range(2):
         n_r = got[r].shape[0]
