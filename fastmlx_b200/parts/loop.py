@@ -49,11 +49,13 @@ class LoopPass(Part):
     def forward(self, delta, residual, ctx, cache):
         e, rt, d = self.entry, self.entry.rt, self.entry.width
         x0 = ctx.scratch["embedding"]
-        joined = ctx.scratch.get("stream beside embeddings")
-        if joined is None:
-            joined = ctx.scratch["stream beside embeddings"] = torch.empty((x0.shape[0], 2 * d), dtype=rt.dtype,
-                                                                            device=x0.device)
+        # one buffer per forward pass, shared by the loop's passes: the embeddings are copied beside the stream's place
+        # once.  A context may be run twice (the warm-up before a capture, then the capture): the copy belongs to each run.
+        made_for, joined = ctx.scratch.get("stream beside embeddings", (None, None))
+        if made_for is not x0:
+            joined = torch.empty((x0.shape[0], 2 * d), dtype=rt.dtype, device=x0.device)
             joined[:, d:].copy_(x0)
+            ctx.scratch["stream beside embeddings"] = (x0, joined)
         settle(delta, residual, rt, out=joined[:, :d])
         y = rt.k.linear(joined, e.weight, None, torch.float32)
         return Pending(y, None, 1.0, e.steps[self.index]), None
