@@ -1,23 +1,30 @@
 // Grouped products of a routed feed-forward: every (token, chosen expert) pair multiplies with its own expert's
 // matrices and with no other.
 //
-// fmx_moe_sort lays the pairs out expert by expert: each expert's pairs start on a multiple of BM rows (the rows
+// fmx_moe_sort lays the pairs out expert by expert: each expert's pairs start on a multiple of BM = 128 rows (the rows
 // between are padding and name token -1), so that a tile of BM sorted rows belongs to one expert; it also records
 // where each pair went, the pair's weight in sorted order, and each tile's expert.  One block does it all.  Which of
 // an expert's rows a pair gets depends on the order of atomic additions; no result depends on it, since every row of
 // the products below is computed from that row alone.
 //
-// fmx_moe_grouped_gate_up: tile (m, n) = 64 sorted rows x 64 hidden columns of the tile's expert: G = X W_gate^T and
-// U = X W_up^T side by side (mma.sync m16n8k16, bf16 in, 32-bit sums, cp.async double-buffered tiles of 32 along K),
+// fmx_moe_grouped_gate_up: tile (m, n) = 128 sorted rows x 64 hidden columns of the tile's expert: G = X W_gate^T and
+// U = X W_up^T side by side (mma.sync m16n8k16, bf16 in, 32-bit sums, a three-stage cp.async ring of tiles of 32 along K),
 // and in the epilogue y = w * g' sigmoid(1.702 g') (u' + 1), g' = min(G, limit), u' = clamp(U, -limit, limit), w the
 // pair's weight; rows are gathered from the step's activations by token.  fmx_moe_grouped_down: pair outputs
-// Y W_down^T in 32-bit.  fmx_moe_combine: a token's pair outputs added in the order of its choices, plus the shared
+// Y W_down^T in 32-bit, 128 x 128 per tile.  fmx_moe_combine: a token's pair outputs added in the order of its choices, plus the shared
 // expert's output, rounded once.
 #include <math.h>
 #include "common.cuh"
 
 namespace {
-constexpr int BM = 64, BN = 64, BK = 32, ROWP = BK + 8, THREADS = 128;
+constexpr int BM = 128, BK = 32, ROWP = BK + 8, THREADS = 256, STAGES = 3;
+template <bool GATED> struct Tile {
+  static constexpr int BN = GATED ? 64 : 128;            // hidden columns (of gate and of up), or output columns
+  static constexpr int WM = GATED ? 4 : 2, WN = GATED ? 2 : 4;      // warps along rows and columns
+  static constexpr int MT = BM / WM / 16;                // 16-row tiles of a warp: 2 or 4; a warp spans 32 columns
+  static constexpr int STAGE = (BM + (GATED ? 2 : 1) * BN) * ROWP;  // elements of one stage: A, W0 (, W1)
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE * sizeof(bf16);
+};
 
 __device__ __forceinline__ void cp16(void* smem, const void* gmem, bool valid) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -81,37 +88,40 @@ moe_sort_kernel(const int* chosen, const float* weights, int T, int E, int top, 
   }
 }
 
-// One K step of a warp's 32 x 32 part: A rows [am, am + 32) of `as`, W rows [bn, bn + 32) of `ws`.
-__device__ __forceinline__ void warp_step(float (&acc)[2][4][4], const bf16* as, const bf16* ws, int am, int bn) {
+// One K step (BK) of a warp's (16 MT) x 32 part: A rows [am, ...) of `as`, W rows [bn, bn + 32) of `ws`.
+template <int MT>
+__device__ __forceinline__ void warp_step(float (&acc)[MT][4][4], const bf16* as, const bf16* ws, int am, int bn) {
   const int lane = threadIdx.x & 31, mi = lane >> 3, ri = lane & 7;
 #pragma unroll
   for (int kk = 0; kk < BK; kk += 16) {
-    unsigned a[2][4];
+    unsigned b[2][4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) ldsm4(a[i], as + (am + 16 * i + (mi & 1) * 8 + ri) * ROWP + kk + (mi >> 1) * 8);
+    for (int jp = 0; jp < 2; ++jp)          // matrices: (cols 16jp.., k), (same cols, k + 8), (cols 16jp + 8.., k), (.., k + 8)
+      ldsm4(b[jp], ws + (bn + 16 * jp + (mi >> 1) * 8 + ri) * ROWP + kk + (mi & 1) * 8);
 #pragma unroll
-    for (int jp = 0; jp < 2; ++jp) {
-      unsigned b[4];
-      // matrices: (cols 16jp.., k), (same cols, k + 8), (cols 16jp + 8.., k), (.., k + 8)
-      ldsm4(b, ws + (bn + 16 * jp + (mi >> 1) * 8 + ri) * ROWP + kk + (mi & 1) * 8);
+    for (int i = 0; i < MT; ++i) {
+      unsigned a[4];
+      ldsm4(a, as + (am + 16 * i + (mi & 1) * 8 + ri) * ROWP + kk + (mi >> 1) * 8);
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        mma16816(acc[i][2 * jp], a[i], b[0], b[1]);
-        mma16816(acc[i][2 * jp + 1], a[i], b[2], b[3]);
+      for (int jp = 0; jp < 2; ++jp) {
+        mma16816(acc[i][2 * jp], a, b[jp][0], b[jp][1]);
+        mma16816(acc[i][2 * jp + 1], a, b[jp][2], b[jp][3]);
       }
     }
   }
 }
 
 // GATED: W0 = the expert's gate rows, W1 = its up rows, out = activation (bf16); else W0 alone, out = product (32-bit).
+// Rows of padding are neither read nor written.
 template <bool GATED>
 __global__ void __launch_bounds__(THREADS)
 moe_grouped_kernel(const bf16* a, long long lda, const int* sorted_token, const float* sorted_w, const int* tile_expert,
                    const bf16* w0, const bf16* w1, long long ldw, long long expert_stride, void* out, long long ldo, int N,
                    int K, float limit) {
-  __shared__ __align__(16) bf16 As[2][BM * ROWP];
-  __shared__ __align__(16) bf16 W0s[2][BN * ROWP];
-  __shared__ __align__(16) bf16 W1s[GATED ? 2 : 1][GATED ? BN * ROWP : 8];
+  using TL = Tile<GATED>;
+  constexpr int BN = TL::BN, MT = TL::MT;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   __shared__ int toks[BM];
   pdl_wait();
   pdl_trigger();
@@ -124,27 +134,33 @@ moe_grouped_kernel(const bf16* a, long long lda, const int* sorted_token, const 
   __syncthreads();
   const bf16* we0 = w0 + (long long)e * expert_stride;
   const bf16* we1 = GATED ? w1 + (long long)e * expert_stride : nullptr;
+  auto stage_a = [&](int s) { return smem + (size_t)s * TL::STAGE; };
+  auto stage_w0 = [&](int s) { return smem + (size_t)s * TL::STAGE + BM * ROWP; };
+  auto stage_w1 = [&](int s) { return smem + (size_t)s * TL::STAGE + (BM + BN) * ROWP; };
   auto load = [&](int stage, int k0) {
 #pragma unroll
     for (int it = 0; it < (BM * (BK / 8)) / THREADS; ++it) {
       const int item = tid + it * THREADS;
       const int r = item / (BK / 8), ch = item - r * (BK / 8);
       const int k = k0 + ch * 8;
-      const bool kin = k < K;
-      // rows of A: gathered by token (GATED), or the sorted rows themselves
-      const int tok = toks[r];
+      const int tok = toks[r];                       // rows of A: gathered by token (GATED), or the sorted rows themselves
       const long long arow = GATED ? tok : row0 + r;
-      const bool av = kin && tok >= 0;
-      cp16(&As[stage][r * ROWP + ch * 8], av ? a + arow * lda + k : a, av);
-      const bool wv = kin && n0 + r < N;
-      cp16(&W0s[stage][r * ROWP + ch * 8], wv ? we0 + (long long)(n0 + r) * ldw + k : w0, wv);
-      if (GATED) cp16(&W1s[stage][r * ROWP + ch * 8], wv ? we1 + (long long)(n0 + r) * ldw + k : w0, wv);
+      const bool av = k < K && tok >= 0;
+      cp16(stage_a(stage) + r * ROWP + ch * 8, av ? a + arow * lda + k : a, av);
     }
-    asm volatile("cp.async.commit_group;\n" ::);
-  };
-  float acc0[2][4][4], acc1[GATED ? 2 : 1][4][4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+    for (int it = 0; it < (BN * (BK / 8)) / THREADS; ++it) {
+      const int item = tid + it * THREADS;
+      const int r = item / (BK / 8), ch = item - r * (BK / 8);
+      const int k = k0 + ch * 8;
+      const bool wv = k < K && n0 + r < N;
+      cp16(stage_w0(stage) + r * ROWP + ch * 8, wv ? we0 + (long long)(n0 + r) * ldw + k : w0, wv);
+      if (GATED) cp16(stage_w1(stage) + r * ROWP + ch * 8, wv ? we1 + (long long)(n0 + r) * ldw + k : w0, wv);
+    }
+  };
+  float acc0[MT][4][4], acc1[GATED ? MT : 1][4][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -152,30 +168,33 @@ moe_grouped_kernel(const bf16* a, long long lda, const int* sorted_token, const 
         acc0[i][j][c] = 0.f;
         if (GATED) acc1[i][j][c] = 0.f;
       }
-  const int am = (warp >> 1) * 32, bn = (warp & 1) * 32;
+  const int am = (warp / TL::WN) * (16 * MT), bn = (warp % TL::WN) * 32;
   const int steps = (K + BK - 1) / BK;
-  load(0, 0);
-  for (int s = 0; s < steps; ++s) {
-    if (s + 1 < steps) {
-      load((s + 1) & 1, (s + 1) * BK);
-      asm volatile("cp.async.wait_group 1;\n" ::);
-    } else {
-      asm volatile("cp.async.wait_group 0;\n" ::);
-    }
-    __syncthreads();
-    warp_step(acc0, As[s & 1], W0s[s & 1], am, bn);
-    if (GATED) warp_step(reinterpret_cast<float (&)[2][4][4]>(acc1), As[s & 1], W1s[s & 1], am, bn);
-    __syncthreads();
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < steps) load(s, s * BK);
+    asm volatile("cp.async.commit_group;\n" ::);
   }
+  for (int it = 0; it < steps; ++it) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2));
+    __syncthreads();
+    const int nx = it + STAGES - 1;
+    if (nx < steps) load(nx % STAGES, nx * BK);
+    asm volatile("cp.async.commit_group;\n" ::);
+    const int st = it % STAGES;
+    warp_step<MT>(acc0, stage_a(st), stage_w0(st), am, bn);
+    if (GATED) warp_step<MT>(reinterpret_cast<float (&)[MT][4][4]>(acc1), stage_a(st), stage_w1(st), am, bn);
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::);
   const int gq = lane >> 2, tq = lane & 3;
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < MT; ++i)
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
       const int r = am + 16 * i + gq + 8 * x;
       const long long row = row0 + r;
-      const bool real = toks[r] >= 0;
-      const float w = GATED && real ? sorted_w[row] : 0.f;
+      if (toks[r] < 0) continue;
+      const float w = GATED ? sorted_w[row] : 0.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int n = n0 + bn + 8 * j + 2 * tq;
@@ -183,12 +202,9 @@ moe_grouped_kernel(const bf16* a, long long lda, const int* sorted_token, const 
         for (int c = 0; c < 2; ++c) {
           if (n + c >= N) continue;
           if (GATED) {
-            float y = 0.f;
-            if (real) {
-              const float g = fminf(acc0[i][j][2 * x + c], limit);
-              const float u = fminf(fmaxf(acc1[i][j][2 * x + c], -limit), limit);
-              y = w * (g / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
-            }
+            const float g = fminf(acc0[i][j][2 * x + c], limit);
+            const float u = fminf(fmaxf(acc1[i][j][2 * x + c], -limit), limit);
+            const float y = w * (g / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
             reinterpret_cast<bf16*>(out)[row * ldo + n + c] = __float2bfloat16_rn(y);
           } else {
             reinterpret_cast<float*>(out)[row * ldo + n + c] = acc0[i][j][2 * x + c];
@@ -219,8 +235,8 @@ __global__ void moe_combine_kernel(const float* pair_out, const int* pair_pos, c
 
 FMX_EXPORT int fmx_moe_tile_rows() { return BM; }
 
-// chosen [T, top] (-1: none), weights [T, E]; sorted_token / sorted_w [max_tiles * 64], pair_pos [T * top],
-// tile_expert [max_tiles], max_tiles >= (T * top + E * 63) / 64 rounded up.
+// chosen [T, top] (-1: none), weights [T, E]; sorted_token / sorted_w [max_tiles * R], pair_pos [T * top],
+// tile_expert [max_tiles], R = fmx_moe_tile_rows(), max_tiles >= (T * top + E * (R - 1)) / R rounded up.
 FMX_EXPORT int fmx_moe_sort(const int* chosen, const float* weights, int T, int E, int top, int* sorted_token, float* sorted_w,
                             int* pair_pos, int* tile_expert, int max_tiles, cudaStream_t stream) {
   if (T == 0) return 0;
@@ -245,7 +261,13 @@ FMX_EXPORT int fmx_moe_grouped_gate_up(const void* x, long long ldx, const int* 
       ((uintptr_t)w_up & 15))
     return fmx_fail("fmx_moe_grouped_gate_up: rows of 16 bytes wanted (K=%d)", K);
   if (max_tiles > 65535) return fmx_fail("fmx_moe_grouped_gate_up: too many tiles for one launch");
-  fmx_launch(moe_grouped_kernel<true>, dim3((ff + BN - 1) / BN, max_tiles), dim3(THREADS), 0, stream, (const bf16*)x, ldx, sorted_token,
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<true>::SMEM);
+    if (e != cudaSuccess) return fmx_fail("fmx_moe_grouped_gate_up: shared memory of %zu bytes refused: %s", Tile<true>::SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  fmx_launch(moe_grouped_kernel<true>, dim3((ff + Tile<true>::BN - 1) / Tile<true>::BN, max_tiles), dim3(THREADS), Tile<true>::SMEM, stream, (const bf16*)x, ldx, sorted_token,
              sorted_w, tile_expert, (const bf16*)w_gate, (const bf16*)w_up, ldw, expert_stride, y, (long long)ff, ff, K, limit);
   FMX_LAUNCH_CHECK();
   return 0;
@@ -260,7 +282,13 @@ FMX_EXPORT int fmx_moe_grouped_down(const void* y, const int* sorted_token, cons
   if (ff <= 0 || d <= 0 || ff % 8 || ldw % 8 || expert_stride % 8 || ((uintptr_t)y & 15) || ((uintptr_t)w_down & 15))
     return fmx_fail("fmx_moe_grouped_down: rows of 16 bytes wanted (ff=%d)", ff);
   if (max_tiles > 65535) return fmx_fail("fmx_moe_grouped_down: too many tiles for one launch");
-  fmx_launch(moe_grouped_kernel<false>, dim3((d + BN - 1) / BN, max_tiles), dim3(THREADS), 0, stream, (const bf16*)y, (long long)ff,
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<false>::SMEM);
+    if (e != cudaSuccess) return fmx_fail("fmx_moe_grouped_down: shared memory of %zu bytes refused: %s", Tile<false>::SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  fmx_launch(moe_grouped_kernel<false>, dim3((d + Tile<false>::BN - 1) / Tile<false>::BN, max_tiles), dim3(THREADS), Tile<false>::SMEM, stream, (const bf16*)y, (long long)ff,
              sorted_token, (const float*)nullptr, tile_expert, (const bf16*)w_down, (const bf16*)nullptr, ldw, expert_stride,
              (void*)pair_out, (long long)d, d, ff, 0.f);
   FMX_LAUNCH_CHECK();

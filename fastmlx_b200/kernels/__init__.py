@@ -589,17 +589,18 @@ def moe_expert_act(gu, weights, E: int, ff: int, limit: float, limit_shared: flo
     return out
 
 
-MOE_TILE_ROWS = 64
+MOE_TILE_ROWS = 128         # rows of a tile of sorted pairs (`fmx_moe_tile_rows` of the library)
 
 
 def moe_sort(chosen, weights):
-    """The (token, chosen expert) pairs laid out expert by expert, each expert's pairs starting on a multiple of 64
-    rows.  chosen int32 [T, top] (-1: none), weights 32-bit [T, E].  -> a plan for the grouped products: (token of each
-    sorted row or -1, weight of each sorted row, sorted row of each pair, expert of each tile of 64 rows or -1, tiles)."""
+    """The (token, chosen expert) pairs laid out expert by expert, each expert's pairs starting on a multiple of
+    MOE_TILE_ROWS rows.  chosen int32 [T, top] (-1: none), weights 32-bit [T, E].  -> a plan for the grouped products: (token of each
+    sorted row or -1, weight of each sorted row, sorted row of each pair, expert of each tile of rows or -1, tiles)."""
     _need_cuda(chosen, weights)
     T, top = chosen.shape
     E = weights.shape[1]
     assert chosen.dtype == torch.int32 and chosen.is_contiguous() and weights.dtype == torch.float32 and weights.is_contiguous()
+    assert int(load("bf16").fmx_moe_tile_rows()) == MOE_TILE_ROWS
     tiles = -(-(T * top + E * (MOE_TILE_ROWS - 1)) // MOE_TILE_ROWS)
     dev = chosen.device
     sorted_token = torch.empty(tiles * MOE_TILE_ROWS, dtype=torch.int32, device=dev)
@@ -614,7 +615,7 @@ def moe_sort(chosen, weights):
 def moe_grouped_gate_up(x, plan, gate_up, E: int, ff: int, limit: float) -> torch.Tensor:
     """The experts' hidden layers for the sorted pairs of `plan`: gate_up [2 E ff, K] bfloat16 holds every expert's gate
     rows and then every expert's up rows; row r of the result is w g' sigmoid(1.702 g') (u' + 1) of the row's token under
-    the row's expert (clamped by `limit`, scaled by the pair's weight); padding rows are zero.  -> bfloat16 [tiles * 64, ff]."""
+    the row's expert (clamped by `limit`, scaled by the pair's weight); padding rows are not written.  -> bfloat16 [tiles * MOE_TILE_ROWS, ff]."""
     sorted_token, sorted_w, _, tile_expert, tiles = plan
     _need_cuda(x, gate_up)
     K = x.shape[1]
@@ -628,7 +629,8 @@ def moe_grouped_gate_up(x, plan, gate_up, E: int, ff: int, limit: float) -> torc
 
 
 def moe_grouped_down(y, plan, down, E: int, ff: int) -> torch.Tensor:
-    """The pairs' outputs: down [d, E ff] bfloat16 holds the experts' down matrices side by side.  -> 32-bit [tiles * 64, d]."""
+    """The pairs' outputs: down [d, E ff] bfloat16 holds the experts' down matrices side by side.  -> 32-bit [tiles * MOE_TILE_ROWS, d]
+    (padding rows are not written)."""
     sorted_token, _, _, tile_expert, tiles = plan
     d = down.shape[0]
     assert down.dtype == torch.bfloat16 and down.is_contiguous() and down.shape[1] == E * ff and y.is_contiguous()
