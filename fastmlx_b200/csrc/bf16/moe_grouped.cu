@@ -42,7 +42,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], 
 
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(const int* chosen, const float* weights, int T, int E, int top, int* sorted_token, float* sorted_w,
-                int* pair_pos, int* tile_expert, int max_tiles) {
+                int* pair_pos, int* tile_expert, int max_tiles, int* used_rows) {
   extern __shared__ int sm[];                   // counts[E], offsets[E + 1], cursor[E]
   int* counts = sm;
   int* offsets = sm + E;
@@ -67,6 +67,7 @@ moe_sort_kernel(const int* chosen, const float* weights, int T, int E, int top, 
   }
   __syncthreads();
   const int used = offsets[E];
+  if (threadIdx.x == 0 && used_rows != nullptr) *used_rows = min(used, max_tiles * BM);
   for (int i = threadIdx.x; i < max_tiles * BM; i += blockDim.x) sorted_token[i] = -1;
   for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
   __syncthreads();
@@ -117,7 +118,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(THREADS)
 moe_grouped_kernel(const bf16* a, long long lda, const int* sorted_token, const float* sorted_w, const int* tile_expert,
                    const bf16* w0, const bf16* w1, long long ldw, long long expert_stride, void* out, long long ldo, int N,
-                   int K, float limit) {
+                   int K, float limit, int block) {
   using TL = Tile<GATED>;
   constexpr int BN = TL::BN, MT = TL::MT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -154,8 +155,10 @@ moe_grouped_kernel(const bf16* a, long long lda, const int* sorted_token, const 
       const int r = item / (BK / 8), ch = item - r * (BK / 8);
       const int k = k0 + ch * 8;
       const bool wv = k < K && n0 + r < N;
-      cp16(stage_w0(stage) + r * ROWP + ch * 8, wv ? we0 + (long long)(n0 + r) * ldw + k : w0, wv);
-      if (GATED) cp16(stage_w1(stage) + r * ROWP + ch * 8, wv ? we1 + (long long)(n0 + r) * ldw + k : w0, wv);
+      // block > 0: the expert's rows come in blocks of `block` gate rows followed by their `block` up rows
+      const long long wrow = block > 0 ? (long long)((n0 + r) / block) * 2 * block + (n0 + r) % block : n0 + r;
+      cp16(stage_w0(stage) + r * ROWP + ch * 8, wv ? we0 + wrow * ldw + k : w0, wv);
+      if (GATED) cp16(stage_w1(stage) + r * ROWP + ch * 8, wv ? we1 + wrow * ldw + k : w0, wv);
     }
   };
   float acc0[MT][4][4], acc1[GATED ? MT : 1][4][4];
@@ -233,29 +236,55 @@ __global__ void moe_combine_kernel(const float* pair_out, const int* pair_pos, c
 }
 }  // namespace
 
+namespace {
+// out[r] = x[sorted_token[r]], zeros for a row of padding; rows of 16-byte pieces.
+__global__ void moe_gather_kernel(const bf16* x, long long ldx, const int* sorted_token, const int* used_rows, bf16* out, int K) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x;
+  if (r >= *used_rows) return;
+  const int tok = sorted_token[r];
+  const uint4* src = reinterpret_cast<const uint4*>(x + (long long)max(tok, 0) * ldx);
+  uint4* dst = reinterpret_cast<uint4*>(out + (long long)r * K);
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = tok >= 0 ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+}
+}  // namespace
+
 FMX_EXPORT int fmx_moe_tile_rows() { return BM; }
 
+// The pairs' inputs in sorted order for a product that reads its rows in place: out [max_rows, K].
+FMX_EXPORT int fmx_moe_gather(const void* x, long long ldx, const int* sorted_token, const int* used_rows, void* out, int max_rows,
+                              int K, cudaStream_t stream) {
+  if (max_rows <= 0) return 0;
+  if (K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return fmx_fail("fmx_moe_gather: rows of 16 bytes wanted (K=%d)", K);
+  fmx_launch(moe_gather_kernel, dim3(max_rows), dim3(128), 0, stream, (const bf16*)x, ldx, sorted_token, used_rows, (bf16*)out, K);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
 // chosen [T, top] (-1: none), weights [T, E]; sorted_token / sorted_w [max_tiles * R], pair_pos [T * top],
-// tile_expert [max_tiles], R = fmx_moe_tile_rows(), max_tiles >= (T * top + E * (R - 1)) / R rounded up.
+// tile_expert [max_tiles], R = fmx_moe_tile_rows(), max_tiles >= (T * top + E * (R - 1)) / R rounded up; used_rows [1]: the
+// sorted rows in use (every tile below used_rows / R has an expert; the experts' runs follow one another).
 FMX_EXPORT int fmx_moe_sort(const int* chosen, const float* weights, int T, int E, int top, int* sorted_token, float* sorted_w,
-                            int* pair_pos, int* tile_expert, int max_tiles, cudaStream_t stream) {
+                            int* pair_pos, int* tile_expert, int max_tiles, int* used_rows, cudaStream_t stream) {
   if (T == 0) return 0;
   if (T < 0 || E <= 0 || top <= 0 || (long long)max_tiles * BM < (long long)T * top + (long long)E * (BM - 1))
     return fmx_fail("fmx_moe_sort: bad sizes T=%d E=%d top=%d tiles=%d", T, E, top, max_tiles);
   const size_t smem = (3 * (size_t)E + 1) * sizeof(int);
   if (smem > 48 * 1024) return fmx_fail("fmx_moe_sort: %d experts are more than the kernel's shared memory holds", E);
   fmx_launch(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, chosen, weights, T, E, top, sorted_token, sorted_w, pair_pos,
-             tile_expert, max_tiles);
+             tile_expert, max_tiles, used_rows);
   FMX_LAUNCH_CHECK();
   return 0;
 }
 
 // x [T, K] bf16 (rows of ldx); w_gate / w_up: expert e's rows start e * expert_stride elements in, rows of ldw;
 // y [max_tiles * 64, ff] bf16.
+// block > 0: gate and up rows alternate in blocks of `block` (w_up = w_gate + block rows).
 FMX_EXPORT int fmx_moe_grouped_gate_up(const void* x, long long ldx, const int* sorted_token, const float* sorted_w,
                                        const int* tile_expert, const void* w_gate, const void* w_up, long long ldw,
                                        long long expert_stride, void* y, int max_tiles, int ff, int K, float limit,
-                                       cudaStream_t stream) {
+                                       int block, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
   if (ff <= 0 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || expert_stride % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w_gate & 15) ||
       ((uintptr_t)w_up & 15))
@@ -268,7 +297,7 @@ FMX_EXPORT int fmx_moe_grouped_gate_up(const void* x, long long ldx, const int* 
     configured = true;
   }
   fmx_launch(moe_grouped_kernel<true>, dim3((ff + Tile<true>::BN - 1) / Tile<true>::BN, max_tiles), dim3(THREADS), Tile<true>::SMEM, stream, (const bf16*)x, ldx, sorted_token,
-             sorted_w, tile_expert, (const bf16*)w_gate, (const bf16*)w_up, ldw, expert_stride, y, (long long)ff, ff, K, limit);
+             sorted_w, tile_expert, (const bf16*)w_gate, (const bf16*)w_up, ldw, expert_stride, y, (long long)ff, ff, K, limit, block);
   FMX_LAUNCH_CHECK();
   return 0;
 }
@@ -290,7 +319,7 @@ FMX_EXPORT int fmx_moe_grouped_down(const void* y, const int* sorted_token, cons
   }
   fmx_launch(moe_grouped_kernel<false>, dim3((d + Tile<false>::BN - 1) / Tile<false>::BN, max_tiles), dim3(THREADS), Tile<false>::SMEM, stream, (const bf16*)y, (long long)ff,
              sorted_token, (const float*)nullptr, tile_expert, (const bf16*)w_down, (const bf16*)nullptr, ldw, expert_stride,
-             (void*)pair_out, (long long)d, d, ff, 0.f);
+             (void*)pair_out, (long long)d, d, ff, 0.f, 0);
   FMX_LAUNCH_CHECK();
   return 0;
 }

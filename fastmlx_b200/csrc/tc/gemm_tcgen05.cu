@@ -35,7 +35,22 @@ using namespace fmx_tc;
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
 
-enum Epilogue { EPI_PLAIN = 0, EPI_SILU_MUL = 1, EPI_RESIDUAL = 2, EPI_RELU2 = 3 };   // RELU2: max(x, 0)^2
+// RELU2: max(x, 0)^2.  EXPERT: a routed expert's gated activation, w g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit),
+// u' = clamp(u, -limit, limit) and w the row's weight, over gate/up blocks like SILU_MUL.  F32: the product as 32-bit floats.
+enum Epilogue { EPI_PLAIN = 0, EPI_SILU_MUL = 1, EPI_RESIDUAL = 2, EPI_RELU2 = 3, EPI_EXPERT = 4, EPI_F32 = 5 };
+
+// A grouped product: the rows of A are (token, expert) pairs sorted expert by expert, each expert's rows starting on a
+// multiple of 128, and tile row m multiplies with the matrix of expert tile_expert[m], which lies expert_rows rows further
+// down W per expert.  used_rows (on the device: the sort ran just before) says how many rows are in use; rows whose
+// row_token is negative are padding and are not written.  All null / 0: an ordinary product.
+struct Grouped {
+  const int* used_rows;
+  const int* tile_expert;
+  const int* row_token;
+  const float* row_weight;
+  int expert_rows;
+  float limit;
+};
 
 template <int BN> struct Cfg {
   static constexpr int STAGES = BN == 256 ? 4 : (BN == 192 ? 5 : 6);
@@ -55,7 +70,7 @@ __device__ __forceinline__ float silu(float g) { return g / (1.0f + expf(-g)); }
 template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, bf16* C,
-                    long long ldc, const bf16* residual, long long ldr, int M, int N, int K, int* status) {
+                    long long ldc, const bf16* residual, long long ldr, int M_max, int N, int K, int* status, Grouped gr) {
   using cfg = Cfg<BN>;
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment: the swizzle pattern repeats every eight 128-byte rows
@@ -69,8 +84,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int n_tiles = tiles_m * tiles_n;
+  const int tiles_n = (N + BN - 1) / BN;
   const int k_blocks = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -96,6 +110,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();                                      // A is the output of the kernel before this one
   pdl_trigger();
+  int M = M_max;
+  if (gr.used_rows != nullptr) M = min(M_max, *gr.used_rows);      // a grouped product: the rows in use, as the sort left them
+  const int tiles_m = (M + BM - 1) / BM;
+  const int n_tiles = tiles_m * tiles_n;
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------------ producer
@@ -104,7 +122,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     long long issued = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-      const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+      const int m0 = (t % tiles_m) * BM;
+      int n0 = (t / tiles_m) * BN;
+      if (gr.tile_expert != nullptr) n0 += max(0, gr.tile_expert[m0 / BM]) * gr.expert_rows;      // this tile's expert's rows of W
       for (int kb = 0; kb < k_blocks; ++kb) {
 #ifdef FMX_SKIP_LAST_STAGE
         if (kb == k_blocks - 1 && t + (int)gridDim.x >= n_tiles) break;      // the test build: never bring the last block
@@ -182,7 +202,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    constexpr int OUT_COLS = EPI == EPI_SILU_MUL ? BN / 2 : BN;
+    constexpr bool GATED = EPI == EPI_SILU_MUL || EPI == EPI_EXPERT;
+    constexpr int OUT_COLS = GATED ? BN / 2 : BN;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
       const int m0 = (t % tiles_m) * BM, n_tile = t / tiles_m;
       if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase)) { ok = false; break; }
@@ -190,14 +211,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       const int out_n0 = n_tile * OUT_COLS;
-      const int n_out = EPI == EPI_SILU_MUL ? N / 2 : N;
+      const int n_out = GATED ? N / 2 : N;
+      const bool row_in_use = row < M && (gr.row_token == nullptr || gr.row_token[row] >= 0);
+      const float row_w = (EPI == EPI_EXPERT && row_in_use) ? gr.row_weight[row] : 0.f;
 #pragma unroll 1
       for (int c = 0; c < OUT_COLS; c += 16) {
         uint32_t v[16], u[16];
         tmem_ld16(taddr + c, v);
-        if (EPI == EPI_SILU_MUL) tmem_ld16(taddr + BN / 2 + c, u);
+        if (GATED) tmem_ld16(taddr + BN / 2 + c, u);
         tmem_ld_wait();
-        if (row < M) {
+        if (row_in_use) {
           float f[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -208,6 +231,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               const float w = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[i])));
               f[i] = silu(g) * w;
             }
+            if (EPI == EPI_EXPERT) {
+              const float g = fminf(f[i], gr.limit);
+              const float w = fminf(fmaxf(__uint_as_float(u[i]), -gr.limit), gr.limit);
+              f[i] = row_w * (g / (1.0f + expf(-1.702f * g))) * (w + 1.0f);
+            }
             if (EPI == EPI_RELU2) {
               // as the unfused path rounds: the product to bfloat16 first, then the square of its positive part
               const float p = fmaxf(__bfloat162float(__float2bfloat16_rn(f[i])), 0.f);
@@ -215,6 +243,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
           }
           const int col = out_n0 + c;
+          if (EPI == EPI_F32) {
+            float* dstf = reinterpret_cast<float*>(C) + (long long)row * ldc + col;
+            if (col + 16 <= n_out && (((uintptr_t)dstf) & 15) == 0) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) reinterpret_cast<float4*>(dstf)[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (col + i < n_out) dstf[i] = f[i];
+            }
+            continue;
+          }
           bf16* dst = C + (long long)row * ldc + col;
           if (EPI == EPI_RESIDUAL) {
             const bf16* rp = residual + (long long)row * ldr + col;
@@ -252,10 +292,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 template <int BN, int EPI>
 int run(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, const void* residual,
-        long long ldr, int M, int N, int K, int sms, int* status, cudaStream_t stream) {
+        long long ldr, int M, int N, int K, int sms, int* status, cudaStream_t stream, Grouped gr = Grouped{}, long long w_rows = 0) {
   using cfg = Cfg<BN>;
   CUtensorMap map_a, map_w;
-  if (make_map_k128(&map_a, A, M, K, lda, BM) || make_map_k128(&map_w, W, N, K, ldw, BN)) return 1;
+  if (make_map_k128(&map_a, A, M, K, lda, BM) || make_map_k128(&map_w, W, w_rows > 0 ? w_rows : N, K, ldw, BN)) return 1;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -267,11 +307,34 @@ int run(const void* A, long long lda, const void* W, long long ldw, void* C, lon
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
   cudaError_t e = fmx_launch(gemm_tcgen05_kernel<BN, EPI>, dim3(grid), dim3(THREADS), cfg::SMEM, stream, map_a, map_w,
-                             (bf16*)C, ldc, (const bf16*)residual, ldr, M, N, K, status);
+                             (bf16*)C, ldc, (const bf16*)residual, ldr, M, N, K, status, gr);
   if (e != cudaSuccess) return fmx_fail("gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
   return 0;
 }
 }  // namespace
+
+// A routed feed-forward's products over sorted pairs (see `Grouped`).  A [max_rows, K] bfloat16: the pairs' inputs in sorted
+// order, max_rows a multiple of 128.  W: `experts` matrices of N rows each, one under the other, K-contiguous.
+// gated != 0: an expert's N = 2 ff rows come in blocks of 128 gate rows followed by their 128 up rows, and C is bfloat16
+// [max_rows, ff]: the expert's activation scaled by the row's weight; else C is 32-bit [max_rows, N]: the product.
+// used_rows, tile_expert, row_token, row_weight: what the sort of the pairs left on the device.
+FMX_EXPORT int fmx_grouped_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int max_rows,
+                                   int N, int K, int experts, const int* used_rows, const int* tile_expert, const int* row_token,
+                                   const float* row_weight, float limit, int gated, int sms, int* status, cudaStream_t stream) {
+  if (max_rows == 0 || N == 0) return 0;
+  if (max_rows < 0 || max_rows % BM || N <= 0 || K <= 0 || experts <= 0)
+    return fmx_fail("fmx_grouped_tcgen05: bad sizes rows=%d N=%d K=%d experts=%d", max_rows, N, K, experts);
+  if (K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
+    return fmx_fail("fmx_grouped_tcgen05: rows must start on 16-byte boundaries (K=%d lda=%lld ldw=%lld)", K, lda, ldw);
+  if (gated && N % 256) return fmx_fail("fmx_grouped_tcgen05: gate/up blocks need 2 ff a multiple of 256, got %d", N);
+  if (used_rows == nullptr || tile_expert == nullptr || row_token == nullptr || (gated && row_weight == nullptr))
+    return fmx_fail("fmx_grouped_tcgen05: the sorted pairs' arrays are missing");
+  if (sms <= 0) sms = fmx_num_sms();
+  const Grouped gr{used_rows, tile_expert, row_token, row_weight, N, limit};
+  if (gated)
+    return run<256, EPI_EXPERT>(A, lda, W, ldw, C, ldc, nullptr, 0, max_rows, N, K, sms, status, stream, gr, (long long)experts * N);
+  return run<256, EPI_F32>(A, lda, W, ldw, C, ldc, nullptr, 0, max_rows, N, K, sms, status, stream, gr, (long long)experts * N);
+}
 
 // The tile width (of 128, 192, 256) whose tiles fill the SMs' rounds best; wider wins ties.
 FMX_EXPORT int fmx_gemm_tcgen05_plan_width(int M, int N, int sms) {

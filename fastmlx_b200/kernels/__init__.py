@@ -595,7 +595,8 @@ MOE_TILE_ROWS = 128         # rows of a tile of sorted pairs (`fmx_moe_tile_rows
 def moe_sort(chosen, weights):
     """The (token, chosen expert) pairs laid out expert by expert, each expert's pairs starting on a multiple of
     MOE_TILE_ROWS rows.  chosen int32 [T, top] (-1: none), weights 32-bit [T, E].  -> a plan for the grouped products: (token of each
-    sorted row or -1, weight of each sorted row, sorted row of each pair, expert of each tile of rows or -1, tiles)."""
+    sorted row or -1, weight of each sorted row, sorted row of each pair, expert of each tile of rows or -1, tiles, the
+    number of sorted rows in use as a device scalar)."""
     _need_cuda(chosen, weights)
     T, top = chosen.shape
     E = weights.shape[1]
@@ -607,35 +608,64 @@ def moe_sort(chosen, weights):
     sorted_w = torch.empty(tiles * MOE_TILE_ROWS, dtype=torch.float32, device=dev)
     pair_pos = torch.empty(T * top, dtype=torch.int32, device=dev)
     tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev)
+    used = torch.empty(1, dtype=torch.int32, device=dev)
     call("bf16", "fmx_moe_sort", chosen.data_ptr(), weights.data_ptr(), T, E, top, sorted_token.data_ptr(), sorted_w.data_ptr(),
-         pair_pos.data_ptr(), tile_expert.data_ptr(), tiles, _stream())
-    return sorted_token, sorted_w, pair_pos, tile_expert, tiles
+         pair_pos.data_ptr(), tile_expert.data_ptr(), tiles, used.data_ptr(), _stream())
+    return sorted_token, sorted_w, pair_pos, tile_expert, tiles, used
 
 
-def moe_grouped_gate_up(x, plan, gate_up, E: int, ff: int, limit: float) -> torch.Tensor:
-    """The experts' hidden layers for the sorted pairs of `plan`: gate_up [2 E ff, K] bfloat16 holds every expert's gate
-    rows and then every expert's up rows; row r of the result is w g' sigmoid(1.702 g') (u' + 1) of the row's token under
-    the row's expert (clamped by `limit`, scaled by the pair's weight); padding rows are not written.  -> bfloat16 [tiles * MOE_TILE_ROWS, ff]."""
-    sorted_token, sorted_w, _, tile_expert, tiles = plan
+MOE_BLOCK = 128           # gate and up rows of an expert alternate in blocks of this many where its width allows
+MOE_TC_MIN_TOKENS = 128   # steps of at least this many tokens run their grouped products on the tcgen05 kernel
+
+
+def moe_grouped_gate_up(x, plan, gate_up, E: int, ff: int, limit: float, block: int = 0, status=None) -> torch.Tensor:
+    """The experts' hidden layers for the sorted pairs of `plan`.  gate_up [2 E ff, K] bfloat16: with block = 0 every
+    expert's gate rows and then every expert's up rows; with block = MOE_BLOCK expert after expert, each in blocks of
+    `block` gate rows followed by their up rows.  Row r of the result is w g' sigmoid(1.702 g') (u' + 1) of the row's token
+    under the row's expert (clamped by `limit`, scaled by the pair's weight); padding rows are not written.
+    -> bfloat16 [tiles * MOE_TILE_ROWS, ff].  Steps of MOE_TC_MIN_TOKENS tokens and more, with blocked weights, gather the
+    pairs' inputs and multiply on the tcgen05 tensor cores; the others on the tiled mma.sync kernel, which gathers itself."""
+    sorted_token, sorted_w, _, tile_expert, tiles, used = plan
     _need_cuda(x, gate_up)
-    K = x.shape[1]
+    T, K = x.shape
     assert x.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16 and gate_up.is_contiguous() and x.stride(1) == 1
-    assert gate_up.shape == (2 * E * ff, K)
-    y = torch.empty((tiles * MOE_TILE_ROWS, ff), dtype=torch.bfloat16, device=x.device)
+    assert gate_up.shape == (2 * E * ff, K) and block in (0, MOE_BLOCK) and (block == 0 or ff % block == 0)
+    rows = tiles * MOE_TILE_ROWS
+    y = torch.empty((rows, ff), dtype=torch.bfloat16, device=x.device)
+    if block and T >= MOE_TC_MIN_TOKENS and ff % 8 == 0:
+        xs = torch.empty((rows, K), dtype=torch.bfloat16, device=x.device)
+        call("bf16", "fmx_moe_gather", x.data_ptr(), x.stride(0), sorted_token.data_ptr(), used.data_ptr(), xs.data_ptr(), rows, K,
+             _stream())
+        call("tc", "fmx_grouped_tcgen05", xs.data_ptr(), K, gate_up.data_ptr(), K, y.data_ptr(), ff, rows, 2 * ff, K, E,
+             used.data_ptr(), tile_expert.data_ptr(), sorted_token.data_ptr(), sorted_w.data_ptr(), float(limit), 1,
+             num_sms(x.device), _ptr(status if status is not None else _status_word(x.device)), _stream())
+        return y
+    if block:
+        w_up, stride = gate_up.data_ptr() + 2 * block * K, 2 * ff * K
+    else:
+        w_up, stride = gate_up.data_ptr() + 2 * E * ff * K, ff * K
     call("bf16", "fmx_moe_grouped_gate_up", x.data_ptr(), x.stride(0), sorted_token.data_ptr(), sorted_w.data_ptr(),
-         tile_expert.data_ptr(), gate_up.data_ptr(), gate_up.data_ptr() + 2 * E * ff * K, K, ff * K, y.data_ptr(), tiles, ff, K,
-         float(limit), _stream())
+         tile_expert.data_ptr(), gate_up.data_ptr(), w_up, K, stride, y.data_ptr(), tiles, ff, K, float(limit), int(block), _stream())
     return y
 
 
-def moe_grouped_down(y, plan, down, E: int, ff: int) -> torch.Tensor:
-    """The pairs' outputs: down [d, E ff] bfloat16 holds the experts' down matrices side by side.  -> 32-bit [tiles * MOE_TILE_ROWS, d]
-    (padding rows are not written)."""
-    sorted_token, _, _, tile_expert, tiles = plan
-    d = down.shape[0]
-    assert down.dtype == torch.bfloat16 and down.is_contiguous() and down.shape[1] == E * ff and y.is_contiguous()
-    out = torch.empty((tiles * MOE_TILE_ROWS, d), dtype=torch.float32, device=y.device)
-    call("bf16", "fmx_moe_grouped_down", y.data_ptr(), sorted_token.data_ptr(), tile_expert.data_ptr(), down.data_ptr(), E * ff, ff,
+def moe_grouped_down(y, plan, down, E: int, ff: int, stacked: bool = False, tokens: int = 0, status=None) -> torch.Tensor:
+    """The pairs' outputs.  down bfloat16: [d, E ff], the experts' down matrices side by side, or with `stacked`
+    [E d, ff], one under the other.  -> 32-bit [tiles * MOE_TILE_ROWS, d] (padding rows are not written).  `tokens`:
+    the step's tokens (stacked matrices and MOE_TC_MIN_TOKENS of them: the tcgen05 kernel)."""
+    sorted_token, _, _, tile_expert, tiles, used = plan
+    assert down.dtype == torch.bfloat16 and down.is_contiguous() and y.is_contiguous()
+    d = down.shape[0] // E if stacked else down.shape[0]
+    assert down.shape == ((E * d, ff) if stacked else (d, E * ff))
+    rows = tiles * MOE_TILE_ROWS
+    out = torch.empty((rows, d), dtype=torch.float32, device=y.device)
+    if stacked and tokens >= MOE_TC_MIN_TOKENS:
+        call("tc", "fmx_grouped_tcgen05", y.data_ptr(), ff, down.data_ptr(), ff, out.data_ptr(), d, rows, d, ff, E,
+             used.data_ptr(), tile_expert.data_ptr(), sorted_token.data_ptr(), None, 0.0, 0, num_sms(y.device),
+             _ptr(status if status is not None else _status_word(y.device)), _stream())
+        return out
+    ldw, stride = (ff, d * ff) if stacked else (E * ff, ff)
+    call("bf16", "fmx_moe_grouped_down", y.data_ptr(), sorted_token.data_ptr(), tile_expert.data_ptr(), down.data_ptr(), ldw, stride,
          out.data_ptr(), tiles, d, ff, _stream())
     return out
 

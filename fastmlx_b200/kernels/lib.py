@@ -53,13 +53,15 @@ _SIGNATURES = {
     "bf16": {
         "fmx_gemv": [_P, _L, _P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P],
         "fmx_gemv_argmax": [_P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _P],
-        "fmx_moe_sort": [_P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _P],
-        "fmx_moe_grouped_gate_up": [_P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _I, _I, _I, _F, _P],
+        "fmx_moe_sort": [_P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _P, _P],
+        "fmx_moe_gather": [_P, _L, _P, _P, _P, _I, _I, _P],
+        "fmx_moe_grouped_gate_up": [_P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _I, _I, _I, _F, _I, _P],
         "fmx_moe_grouped_down": [_P, _P, _P, _P, _L, _L, _P, _I, _I, _I, _P],
         "fmx_moe_combine": [_P, _P, _P, _L, _I, _P, _L, _I, _I, _I, _I, _P],
     },
     "tc": {
         "fmx_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],
+        "fmx_grouped_tcgen05": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _F, _I, _I, _P, _P],
     },
     "attn": {
         "fmx_attn_prefill_tc": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _I, _P, _L, _P],

@@ -80,8 +80,19 @@ class RoutedExperts(FeedForward):
         if self.sparse and self.shared_ff:        # the shared expert is an ordinary gated feed-forward beside the routed ones
             self.shared_gate_up = torch.cat([gates.pop(), ups.pop()], 0).contiguous()
             self.shared_down = downs.pop().contiguous()
-        self.gate_up = torch.cat(gates + ups, 0).contiguous()
-        self.down = torch.cat(downs, 1).contiguous()
+        # grouped products of wide experts: expert after expert, gate and up rows in alternating blocks (a tile of the
+        # tcgen05 product then holds gates and their ups), down matrices one under the other (rows of ff for its TMA)
+        mb = int(getattr(rt.k, "MOE_BLOCK", 0) or 0)
+        self.block = mb if self.sparse and mb and self.ff % mb == 0 else 0
+        if self.block:
+            b = self.block
+            per = [torch.stack([g.view(-1, b, self.width), u.view(-1, b, self.width)], 1).reshape(-1, self.width)
+                   for g, u in zip(gates, ups)]
+            self.gate_up = torch.cat(per, 0).contiguous()
+            self.down = torch.cat(downs, 0).contiguous()
+        else:
+            self.gate_up = torch.cat(gates + ups, 0).contiguous()
+            self.down = torch.cat(downs, 1).contiguous()
 
     def weight_bytes(self):
         """Bytes a step reads when every expert is used (a decode step of a few tokens reads fewer with grouped products)."""
@@ -115,8 +126,8 @@ class RoutedExperts(FeedForward):
         k, T = self.rt.k, x.shape[0]
         w, chosen = k.moe_route(k.linear(x, self.router, None, torch.float32), self.top, self.groups, self.keep, want_chosen=True)
         plan = k.moe_sort(chosen, w)
-        y = k.moe_grouped_gate_up(x, plan, self.gate_up, self.E, self.ff, self.limit)
-        pairs = k.moe_grouped_down(y, plan, self.down, self.E, self.ff)
+        y = k.moe_grouped_gate_up(x, plan, self.gate_up, self.E, self.ff, self.limit, self.block)
+        pairs = k.moe_grouped_down(y, plan, self.down, self.E, self.ff, stacked=bool(self.block), tokens=T)
         shared = None
         if self.shared_gate_up is not None:
             gu = k.linear(x, self.shared_gate_up, None, self.rt.dtype)

@@ -239,12 +239,14 @@ def test_expert_activation_and_products_per_head(dtype):
         assert torch.allclose(got.cpu().double(), want, atol=tol, rtol=tol)
 
 
-@pytest.mark.parametrize("E,top,ff,groups,keep,shared", [(8, 2, 24, 4, 2, 40), (6, 3, 64, 1, 1, 0), (16, 4, 8, 8, 3, 8), (3, 1, 136, 1, 1, 16)])
-@pytest.mark.parametrize("T", [1, 5, 70, 333])
+@pytest.mark.parametrize("E,top,ff,groups,keep,shared", [(8, 2, 24, 4, 2, 40), (6, 3, 64, 1, 1, 0), (16, 4, 8, 8, 3, 8), (3, 1, 136, 1, 1, 16),
+                                                           (4, 2, 128, 1, 1, 0), (8, 2, 256, 4, 2, 40)])
+@pytest.mark.parametrize("T", [1, 5, 70, 333, 700])
 def test_grouped_products_of_the_routed_experts(E, top, ff, groups, keep, shared, T):
-    """The path of large experts on small ones: pairs sorted expert by expert on the device, tiles of 64 pairs against
+    """The path of large experts on small ones: pairs sorted expert by expert on the device, tiles of pairs against
     their expert's matrices, outputs added per token; against the plain feed-forward and against the path that runs
-    all experts side by side."""
+    all experts side by side.  Experts whose width is a multiple of 128 keep their rows in blocks, and steps of 128 tokens
+    and more multiply them on the tcgen05 kernel."""
     from fastmlx_b200.engine.loading import make_runtime
     from fastmlx_b200.parts import RoutedExperts
     d = 72
