@@ -123,6 +123,38 @@ def test_long_decoding_moves_the_windows_over_decoded_tokens(models, dtype):
     _compare(steps, outs, sub, ref, TOL[dtype], {"r3": CLOSE[("G2", "r3")]} if dtype == "bfloat16" else None)
 
 
+@pytest.mark.parametrize("name", ["G2", "G3"])
+def test_long_portions_read_keys_and_values_out_of_the_latents(models, name):
+    """Portions of 128 tokens and more take latent attention's other form in bfloat16 (keys and values of the tokens in
+    sight read out of the cached latents, for the step): whole prompts, two long portions, a long portion behind a
+    short one, and a long portion beside single tokens of another request, against the plain model."""
+    d, W, _, _ = models[name]
+    cfg = tg.CONFIGS[name]
+    prompts = {"a": tiny.rand_tokens(300, cfg["vocab"], 71), "b": tiny.rand_tokens(200, cfg["vocab"], 72)}
+    ref, skip = {}, {}
+    for r, t in prompts.items():
+        margins = []
+        ref[r] = pg.forward(cfg, W, t, margins=margins)
+        skip[r] = torch.stack(margins).min(0).values < CLOSE_CALL
+    a, b = prompts["a"], prompts["b"]
+
+    def entry(rid, toks):
+        return {"id": rid, "tokens": toks, "want": list(range(len(toks)))}
+
+    schedules = {
+        "whole": traces.whole(prompts),
+        "portions": [{"step": 0, "entries": [entry("a", a[:130])], "end": []}, {"step": 1, "entries": [entry("a", a[130:])], "end": ["a"]},
+                     {"step": 2, "entries": [entry("b", b[:7])], "end": []}, {"step": 3, "entries": [entry("b", b[7:])], "end": ["b"]}],
+        "mixed": [{"step": 0, "entries": [entry("b", b[:190])], "end": []}] +
+                 [{"step": 1 + i, "entries": [entry("b", [b[190 + i]]), entry("a", a[150 * i:150 * (i + 1)])], "end": ["a"] if i == 1 else []}
+                  for i in range(2)] +
+                 [{"step": 3 + i, "entries": [entry("b", [b[192 + i]])], "end": ["b"] if i == 7 else []} for i in range(8)],
+    }
+    for cut, steps in schedules.items():
+        outs, _ = _run(d, "bfloat16", steps, 640, 16)
+        _compare(steps, outs, prompts, ref, TOL["bfloat16"], skip)
+
+
 # ----------------------------------------------------------------------------- kernels alone
 def _k():
     from fastmlx_b200 import kernels
