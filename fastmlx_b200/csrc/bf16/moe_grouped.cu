@@ -248,6 +248,36 @@ __global__ void moe_gather_kernel(const bf16* x, long long ldx, const int* sorte
   uint4* dst = reinterpret_cast<uint4*>(out + (long long)r * K);
   for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = tok >= 0 ? src[i] : make_uint4(0u, 0u, 0u, 0u);
 }
+// The same for bfloat16 rows, four columns per thread.
+__global__ void moe_combine_vec_kernel(const float* pair_out, const int* pair_pos, const bf16* shared, long long shared_stride,
+                                       bf16* out, long long out_stride, long long T, int d, int top) {
+  pdl_wait();
+  pdl_trigger();
+  const int d4 = d / 4;
+  const long long n = T * d4;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / d4;
+    const int c = (int)(idx - t * d4) * 4;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (shared != nullptr) {
+      const uint2 u = *reinterpret_cast<const uint2*>(shared + t * shared_stride + c);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+      s = make_float4(a.x, a.y, b.x, b.y);
+    }
+    for (int k = 0; k < top; ++k) {
+      const int pos = pair_pos[t * top + k];
+      if (pos < 0) continue;
+      const float4 p = *reinterpret_cast<const float4*>(pair_out + (long long)pos * d + c);
+      s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(s.x, s.y), hi = __floats2bfloat162_rn(s.z, s.w);
+    uint2 o;
+    o.x = *reinterpret_cast<unsigned*>(&lo);
+    o.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(out + t * out_stride + c) = o;
+  }
+}
 }  // namespace
 
 FMX_EXPORT int fmx_moe_tile_rows() { return BM; }
@@ -330,9 +360,18 @@ FMX_EXPORT int fmx_moe_combine(const float* pair_out, const int* pair_pos, const
                                int shared_dtype, void* out, long long out_stride, int out_dtype, int T, int d, int top,
                                cudaStream_t stream) {
   if (T == 0) return 0;
-  const long long n = (long long)T * d, cap = (long long)fmx_num_sms() * 16;
+  const int sdt = shared != nullptr ? shared_dtype : out_dtype;
+  const bool vec = out_dtype == FMX_BF16 && sdt == FMX_BF16 && d % 4 == 0 && out_stride % 4 == 0 && shared_stride % 4 == 0 &&
+                   ((uintptr_t)pair_out & 15) == 0 && ((uintptr_t)out & 7) == 0 && ((uintptr_t)shared & 7) == 0;
+  const long long n = (long long)T * (vec ? d / 4 : d), cap = (long long)fmx_num_sms() * 16;
   const int block = 256;
   const int grid = (int)((n + block - 1) / block < cap ? (n + block - 1) / block : cap);
+  if (vec) {
+    fmx_launch(moe_combine_vec_kernel, dim3(grid), dim3(block), 0, stream, pair_out, pair_pos, (const bf16*)shared, shared_stride,
+               (bf16*)out, out_stride, (long long)T, d, top);
+    FMX_LAUNCH_CHECK();
+    return 0;
+  }
 #define FMX_MC(TO, TS)                                                                                                 \
   fmx_launch(moe_combine_kernel<TO, TS>, dim3(grid), dim3(block), 0, stream, pair_out, pair_pos, (const TS*)shared, shared_stride, \
              (TO*)out, out_stride, (long long)T, d, top)

@@ -117,6 +117,38 @@ __global__ void moe_expert_act_kernel(const T* gu, long long gu_stride, const fl
     out[r * out_stride + c] = from_f<T>(y);
   }
 }
+// The same for bfloat16 rows in 16-byte pieces (eight columns of one expert: ff is a multiple of 8).
+__global__ void moe_expert_act_vec_kernel(const bf16* gu, long long gu_stride, const float* weights, bf16* out, long long out_stride,
+                                          long long rows, int E, int ff, int F, float limit, float limit_shared) {
+  pdl_wait();
+  pdl_trigger();
+  const int f8 = F / 8;
+  const long long n = rows * f8;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / f8;
+    const int c = (int)(idx - r * f8) * 8;
+    const int e = c / ff;
+    const float w = e < E ? weights[r * E + e] : 1.0f;
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if (w != 0.f) {
+      const float lim = e < E ? limit : limit_shared;
+      const uint4 g4 = *reinterpret_cast<const uint4*>(gu + r * gu_stride + c);
+      const uint4 u4 = *reinterpret_cast<const uint4*>(gu + r * gu_stride + F + c);
+      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
+      const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+      __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 g = __bfloat1622float2(gp[i]), u = __bfloat1622float2(up[i]);
+        const float g0 = fminf(g.x, lim), g1 = fminf(g.y, lim);
+        const float u0 = fminf(fmaxf(u.x, -lim), lim), u1 = fminf(fmaxf(u.y, -lim), lim);
+        op[i] = __floats2bfloat162_rn(w * (g0 / (1.0f + expf(-1.702f * g0))) * (u0 + 1.0f),
+                                      w * (g1 / (1.0f + expf(-1.702f * g1))) * (u1 + 1.0f));
+      }
+    }
+    *reinterpret_cast<uint4*>(out + r * out_stride + c) = o;
+  }
+}
 }  // namespace
 
 FMX_EXPORT int fmx_moe_route(const float* z, long long z_stride, int T, int E, int top, int groups, int keep, float* weights,
@@ -139,10 +171,15 @@ FMX_EXPORT int fmx_moe_expert_act(const void* gu, long long gu_stride, const flo
   if (rows == 0 || F == 0) return 0;
   if (rows < 0 || E < 0 || ff <= 0 || F < E * ff || gu_stride < 2LL * F || out_stride < F)
     return fmx_fail("fmx_moe_expert_act: bad sizes rows=%d E=%d ff=%d F=%d", rows, E, ff, F);
-  const long long n = (long long)rows * F, cap = (long long)fmx_num_sms() * 16;
+  const bool vec = dtype == FMX_BF16 && F % 8 == 0 && ff % 8 == 0 && (E * ff) % 8 == 0 && gu_stride % 8 == 0 && out_stride % 8 == 0 &&
+                   ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0;
+  const long long n = (long long)rows * (vec ? F / 8 : F), cap = (long long)fmx_num_sms() * 16;
   const int block = 256;
   const int grid = (int)((n + block - 1) / block < cap ? (n + block - 1) / block : cap);
-  if (dtype == FMX_F32)
+  if (vec)
+    fmx_launch(moe_expert_act_vec_kernel, dim3(grid), dim3(block), 0, stream, (const bf16*)gu, gu_stride, weights, (bf16*)out,
+               out_stride, (long long)rows, E, ff, F, limit, limit_shared);
+  else if (dtype == FMX_F32)
     fmx_launch(moe_expert_act_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gu, gu_stride, weights, (float*)out,
                out_stride, (long long)rows, E, ff, F, limit, limit_shared);
   else if (dtype == FMX_BF16)

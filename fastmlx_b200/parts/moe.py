@@ -132,5 +132,5 @@ class RoutedExperts(FeedForward):
         if self.shared_gate_up is not None:
             gu = k.linear(x, self.shared_gate_up, None, self.rt.dtype)
             none = torch.empty((T, 0), dtype=torch.float32, device=x.device)
-            shared = k.linear(k.moe_expert_act(gu, none, 0, 1, 0.0, self.shared_limit), self.shared_down, None, self.rt.dtype)
+            shared = k.linear(k.moe_expert_act(gu, none, 0, 8, 0.0, self.shared_limit), self.shared_down, None, self.rt.dtype)
         return k.moe_combine(pairs, plan, shared, T, self.top, self.rt.dtype)
