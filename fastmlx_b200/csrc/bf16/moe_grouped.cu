@@ -90,8 +90,9 @@ moe_sort_kernel(const int* chosen, const float* weights, int T, int E, int top, 
 }
 
 // One K step (BK) of a warp's (16 MT) x 32 part: A rows [am, ...) of `as`, W rows [bn, bn + 32) of `ws`.
+// `m_tiles`: how many of the warp's 16-row tiles hold a pair at all (a tile's pairs stand at its start).
 template <int MT>
-__device__ __forceinline__ void warp_step(float (&acc)[MT][4][4], const bf16* as, const bf16* ws, int am, int bn) {
+__device__ __forceinline__ void warp_step(float (&acc)[MT][4][4], const bf16* as, const bf16* ws, int am, int bn, int m_tiles) {
   const int lane = threadIdx.x & 31, mi = lane >> 3, ri = lane & 7;
 #pragma unroll
   for (int kk = 0; kk < BK; kk += 16) {
@@ -101,6 +102,7 @@ __device__ __forceinline__ void warp_step(float (&acc)[MT][4][4], const bf16* as
       ldsm4(b[jp], ws + (bn + 16 * jp + (mi >> 1) * 8 + ri) * ROWP + kk + (mi & 1) * 8);
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
+      if (i >= m_tiles) break;
       unsigned a[4];
       ldsm4(a, as + (am + 16 * i + (mi & 1) * 8 + ri) * ROWP + kk + (mi >> 1) * 8);
 #pragma unroll
@@ -131,8 +133,11 @@ moe_grouped_kernel(const bf16* a, long long lda, const int* sorted_token, const 
   if (e < 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const long long row0 = (long long)tile_m * BM;
-  if (tid < BM) toks[tid] = sorted_token[row0 + tid];
-  __syncthreads();
+  const int tok_mine = tid < BM ? sorted_token[row0 + tid] : -1;
+  if (tid < BM) toks[tid] = tok_mine;
+  // the pairs of a tile stand at its start: a decode step's tiles hold a few, and a warp multiplies only the 16-row
+  // tiles that hold any (the expert's weights stream either way)
+  const int n_real = __syncthreads_count(tok_mine >= 0);
   const bf16* we0 = w0 + (long long)e * expert_stride;
   const bf16* we1 = GATED ? w1 + (long long)e * expert_stride : nullptr;
   auto stage_a = [&](int s) { return smem + (size_t)s * TL::STAGE; };
@@ -172,6 +177,7 @@ moe_grouped_kernel(const bf16* a, long long lda, const int* sorted_token, const 
         if (GATED) acc1[i][j][c] = 0.f;
       }
   const int am = (warp / TL::WN) * (16 * MT), bn = (warp % TL::WN) * 32;
+  const int m_tiles = min(MT, max(0, (n_real - am + 15) / 16));
   const int steps = (K + BK - 1) / BK;
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
@@ -185,8 +191,10 @@ moe_grouped_kernel(const bf16* a, long long lda, const int* sorted_token, const 
     if (nx < steps) load(nx % STAGES, nx * BK);
     asm volatile("cp.async.commit_group;\n" ::);
     const int st = it % STAGES;
-    warp_step<MT>(acc0, stage_a(st), stage_w0(st), am, bn);
-    if (GATED) warp_step<MT>(reinterpret_cast<float (&)[MT][4][4]>(acc1), stage_a(st), stage_w1(st), am, bn);
+    if (m_tiles > 0) {
+      warp_step<MT>(acc0, stage_a(st), stage_w0(st), am, bn, m_tiles);
+      if (GATED) warp_step<MT>(reinterpret_cast<float (&)[MT][4][4]>(acc1), stage_a(st), stage_w1(st), am, bn, m_tiles);
+    }
   }
   asm volatile("cp.async.wait_group 0;\n" ::);
   const int gq = lane >> 2, tq = lane & 3;
