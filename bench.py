@@ -403,7 +403,7 @@ def gekavik_like(shape: dict, layers: int, window: int = 1024) -> dict:
            "expert": {"ff": ff // 8, "limit": 7.0}, "shared": {"ff": ff // 2, "limit": 7.0}}
     att = {"type": "attention", "mlp": mlp,
            "mixer": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
-                     "mask": {"size": window, "keep_first": 4}, "rot": {"dims": hd, "base": 10000.0}}}
+                     "mask": {"size": window, "keep_first": 8}, "rot": {"dims": hd, "base": 10000.0}}}
     lat = {"type": "latent_attention", "mlp": mlp,
            "mixer": {"heads": nh, "dim": hd, "vdim": hd, "q_rank": d // 2, "kv_rank": 256, "scale": hd ** -0.5,
                      "mask": {"size": window}}}

@@ -69,7 +69,7 @@ G3 = {
         layer("attention", attention(8, 2, 64, 16, 0.125, window=1000, keep_first=2, rot=(16, 1000000.0)),
               moe(16, 4, 32, 1.2, groups=(8, 3), shared=(64, 1.2))),
         layer("latent_attention", latent(8, 32, 32, 96, 128, 0.18, window=33)),
-        layer("attention", attention(1, 1, 128, 64, 0.09, window=64, keep_first=0, rot=(128, 20000.0)), moe(2, 1, 128, 0.9)),
+        layer("attention", attention(1, 1, 128, 64, 0.09, window=64, keep_first=0, rot=(128, 50000.0)), moe(2, 1, 128, 0.9)),
     ],
     "loop": {"start": 0, "stop": 2, "times": 3},
 }
