@@ -155,6 +155,29 @@ def test_long_portions_read_keys_and_values_out_of_the_latents(models, name):
         _compare(steps, outs, prompts, ref, TOL["bfloat16"], skip)
 
 
+@pytest.mark.parametrize("name", ["G1", "G3", "G5"])
+def test_replay_with_grouped_expert_products(tmp_path, monkeypatch, name):
+    """The same models with the routed experts' grouped products forced on (they are chosen by size): `mma.sync` tiles for
+    steps below 128 tokens and for experts of any width, the tcgen05 kernel for longer portions over experts in blocks of 128
+    (G5); whole prompts, portions, and mixed batches, in bfloat16 against the plain model."""
+    from fastmlx_b200.parts import RoutedExperts
+    monkeypatch.setattr(RoutedExperts, "SPARSE_MIN_BYTES", 0)
+    cfg = getattr(tg, name)
+    d = tg.make_model_dir(tmp_path, cfg, seed=31)
+    W = tiny.load_plain_weights(d)
+    prompts = {f"r{i}": tiny.rand_tokens(n, cfg["vocab"], 800 + i) for i, n in enumerate([3, 40, 200, 77, 150])}
+    ref, skip = {}, {}
+    for r, t in prompts.items():
+        margins = []
+        ref[r] = pg.forward(cfg, W, t, margins=margins)
+        skip[r] = torch.stack(margins).min(0).values < CLOSE_CALL
+    for cut in ("whole", "portions", "mixed"):
+        steps = CUTS[cut](prompts)
+        outs, rp = _run(d, "bfloat16", steps, 640, 16)
+        assert all(b.ffn is None or b.ffn.sparse for b in rp.model.layers if hasattr(b, "ffn"))
+        _compare(steps, outs, prompts, ref, TOL["bfloat16"], skip)
+
+
 # ----------------------------------------------------------------------------- kernels alone
 def _k():
     from fastmlx_b200 import kernels

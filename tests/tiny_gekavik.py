@@ -83,6 +83,14 @@ G4 = {
     "loop": {"start": 1, "stop": 2, "times": 1},
 }
 CONFIGS = {"G1": G1, "G2": G2, "G3": G3, "G4": G4}
+# experts as wide as a block of the grouped products (128 hidden columns), for the tests that force those products on
+G5 = {
+    "architecture": "Gekavik", "vocab": 150, "width": 128, "residual_mult": 0.5, "norm": {"eps": 1e-5},
+    "layers": [
+        layer("attention", attention(4, 2, 32, 32, 0.2, window=50, keep_first=2, rot=(16, 5000.0)), moe(6, 2, 128, 1.1, shared=(128, 0.9))),
+        layer("latent_attention", latent(4, 32, 32, 64, 64, 0.2, window=45), moe(8, 3, 256, 2.0, groups=(4, 2))),
+    ],
+}
 
 
 def lively_tensors(config, seed, dtype=torch.bfloat16):
