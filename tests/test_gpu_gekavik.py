@@ -174,7 +174,7 @@ def test_replay_with_grouped_expert_products(tmp_path, monkeypatch, name):
     for cut in ("whole", "portions", "mixed"):
         steps = CUTS[cut](prompts)
         outs, rp = _run(d, "bfloat16", steps, 640, 16)
-        assert all(b.ffn is None or b.ffn.sparse for b in rp.model.layers if hasattr(b, "ffn"))
+        assert any(b.ffn is not None and b.ffn.sparse for b in rp.model.layers if hasattr(b, "ffn"))      # where experts outnumber twice the chosen
         _compare(steps, outs, prompts, ref, TOL["bfloat16"], skip)
 
 
