@@ -117,8 +117,9 @@ class LatentAttention(Mixer):
             for b in range(lo // ps, (c + n - 1) // ps + 1):
                 rows.append(r)
                 blks.append(b)
-        rows_t = torch.tensor(rows, dtype=torch.long, device=dev)
-        blks_t = torch.tensor(blks, dtype=torch.long, device=dev)
+        # one copy from pinned memory, so that the host does not fall into step with the device
+        both = torch.tensor([rows, blks], dtype=torch.long, pin_memory=True).to(dev, non_blocking=True)
+        rows_t, blks_t = both[0], both[1]
         pages = g.block_tables[rows_t, blks_t].long().clamp_(min=0)
         latents = cache.kv.view(cache.kv.shape[0], ps, self.kv_rank)[pages]      # [pages in sight, page, kv_rank]
         kv = k.linear(latents.view(-1, self.kv_rank), self.ukv, None, torch.bfloat16)
