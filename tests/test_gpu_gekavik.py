@@ -155,6 +155,25 @@ def test_long_portions_read_keys_and_values_out_of_the_latents(models, name):
         _compare(steps, outs, prompts, ref, TOL["bfloat16"], skip)
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_of_configurations_drawn_from_a_seed(tmp_path, seed, dtype):
+    """Sizes, counts, constants and the order of layers drawn at random: whole prompts and mixed batches against the plain model."""
+    cfg = tg.random_config(seed)
+    d = tg.make_model_dir(tmp_path, cfg, seed=seed)
+    W = tiny.load_plain_weights(d)
+    prompts = {f"r{i}": tiny.rand_tokens(n, cfg["vocab"], 40 * seed + i) for i, n in enumerate([2, 35, 150, 64, 101])}
+    ref, skip = {}, {}
+    for r, t in prompts.items():
+        margins = []
+        ref[r] = pg.forward(cfg, W, t, margins=margins)
+        skip[r] = torch.stack(margins).min(0).values < CLOSE_CALL if margins else torch.zeros(len(t), dtype=torch.bool)
+    for cut in ("whole", "mixed"):
+        steps = CUTS[cut](prompts)
+        outs, _ = _run(d, dtype, steps, 512, 16)
+        _compare(steps, outs, prompts, ref, TOL[dtype], skip if dtype == "bfloat16" else None)
+
+
 @pytest.mark.parametrize("name", ["G1", "G3", "G5"])
 def test_replay_with_grouped_expert_products(tmp_path, monkeypatch, name):
     """The same models with the routed experts' grouped products forced on (they are chosen by size): `mma.sync` tiles for

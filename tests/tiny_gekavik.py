@@ -129,3 +129,43 @@ def make_model_dir(root, config, seed):
         json.dump(config, f)
     st.write_file(os.path.join(d, "model.safetensors"), lively_tensors(config, seed), {"format": "pt"})
     return d
+
+
+def random_config(seed):
+    """A configuration drawn from a seed: every size, count, constant and the order of layers vary."""
+    import random
+    rnd = random.Random(seed)
+    width = rnd.choice([40, 48, 72, 96, 136, 200])
+    n_layers = rnd.randint(2, 4)
+    layers = []
+    for _ in range(n_layers):
+        if rnd.random() < 0.5:
+            kv = rnd.choice([1, 2, 3])
+            heads = kv * rnd.choice([1, 2, 4])
+            dim = rnd.choice([8, 16, 24, 40, 64])
+            vdim = rnd.choice([dim, dim, 16, 48])
+            window = rnd.choice([None, 7, 30, 61, 100])
+            keep = rnd.choice([None, 0, 1, 4, 17, 33]) if window else None
+            rot = rnd.choice([None, (dim, 10000.0), (max(2, dim // 2 // 2 * 2), 300.0)])
+            mixer = ("attention", attention(heads, kv, dim, vdim, rnd.choice([0.1, 0.2, dim ** -0.5]), window, keep, rot))
+        else:
+            dim = rnd.choice([8, 16, 32])
+            mixer = ("latent_attention", latent(rnd.choice([1, 2, 3, 5]), dim, rnd.choice([dim, dim, 24]), rnd.choice([16, 40, 64]),
+                                                rnd.choice([16, 36, 64, 128]), rnd.choice([0.15, 0.25]), rnd.choice([None, 9, 40, 90])))
+        mlp = None
+        if rnd.random() < 0.8:
+            groups = rnd.choice([1, 2, 3, 4])
+            per = rnd.choice([1, 2, 3])
+            keep_g = rnd.randint(1, groups)
+            top = rnd.randint(1, per * keep_g)
+            mlp = moe(groups * per, top, rnd.choice([8, 20, 32, 64]), rnd.choice([0.5, 1.0, 4.0]),
+                      (groups, keep_g) if rnd.random() < 0.7 else None, (rnd.choice([8, 24, 64]), rnd.choice([0.7, 2.0])) if rnd.random() < 0.6 else None)
+            if mlp["router"].get("groups") is None:
+                mlp["router"]["top"] = rnd.randint(1, groups * per)
+        layers.append(layer(mixer[0], mixer[1], mlp))
+    cfg = {"architecture": "Gekavik", "vocab": rnd.choice([61, 100, 257]), "width": width, "residual_mult": rnd.choice([0.25, 0.6, 1.0]),
+           "norm": {"eps": rnd.choice([1e-6, 1e-5])}, "layers": layers}
+    if rnd.random() < 0.7:
+        a = rnd.randint(0, n_layers - 1)
+        cfg["loop"] = {"start": a, "stop": rnd.randint(a + 1, n_layers), "times": rnd.randint(1, 3)}
+    return cfg
