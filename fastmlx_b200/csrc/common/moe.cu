@@ -98,7 +98,7 @@ moe_route_kernel(const float* z, long long z_stride, int T, int E, int top, int 
 
 template <typename T>
 __global__ void moe_expert_act_kernel(const T* gu, long long gu_stride, const float* weights, T* out, long long out_stride,
-                                      long long rows, int E, int ff, int F, float limit, float limit_shared) {
+                                      long long rows, int E, int ff, int F, float limit, float limit_shared, int block) {
   pdl_wait();
   pdl_trigger();
   const long long n = rows * F;
@@ -110,8 +110,11 @@ __global__ void moe_expert_act_kernel(const T* gu, long long gu_stride, const fl
     float y = 0.f;
     if (w != 0.f) {
       const float lim = e < E ? limit : limit_shared;
-      const float g = fminf(to_f(gu[r * gu_stride + c]), lim);
-      const float u = fminf(fmaxf(to_f(gu[r * gu_stride + F + c]), -lim), lim);
+      // block > 0: gate and up values alternate in blocks of `block`; else F gates, then F ups
+      const long long gi = block > 0 ? (long long)(c / block) * 2 * block + c % block : c;
+      const long long ui = block > 0 ? gi + block : (long long)F + c;
+      const float g = fminf(to_f(gu[r * gu_stride + gi]), lim);
+      const float u = fminf(fmaxf(to_f(gu[r * gu_stride + ui]), -lim), lim);
       y = w * (g / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
     }
     out[r * out_stride + c] = from_f<T>(y);
@@ -119,7 +122,7 @@ __global__ void moe_expert_act_kernel(const T* gu, long long gu_stride, const fl
 }
 // The same for bfloat16 rows in 16-byte pieces (eight columns of one expert: ff is a multiple of 8).
 __global__ void moe_expert_act_vec_kernel(const bf16* gu, long long gu_stride, const float* weights, bf16* out, long long out_stride,
-                                          long long rows, int E, int ff, int F, float limit, float limit_shared) {
+                                          long long rows, int E, int ff, int F, float limit, float limit_shared, int block) {
   pdl_wait();
   pdl_trigger();
   const int f8 = F / 8;
@@ -132,8 +135,10 @@ __global__ void moe_expert_act_vec_kernel(const bf16* gu, long long gu_stride, c
     uint4 o = make_uint4(0u, 0u, 0u, 0u);
     if (w != 0.f) {
       const float lim = e < E ? limit : limit_shared;
-      const uint4 g4 = *reinterpret_cast<const uint4*>(gu + r * gu_stride + c);
-      const uint4 u4 = *reinterpret_cast<const uint4*>(gu + r * gu_stride + F + c);
+      const long long gi = block > 0 ? (long long)(c / block) * 2 * block + c % block : c;
+      const long long ui = block > 0 ? gi + block : (long long)F + c;
+      const uint4 g4 = *reinterpret_cast<const uint4*>(gu + r * gu_stride + gi);
+      const uint4 u4 = *reinterpret_cast<const uint4*>(gu + r * gu_stride + ui);
       const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
       const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
       __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
@@ -165,9 +170,11 @@ FMX_EXPORT int fmx_moe_route(const float* z, long long z_stride, int T, int E, i
 }
 
 // ff_shared = F - E * ff columns at the end belong to an expert that every token uses with weight 1.
+// gu_block > 0 (a multiple of 8 that divides F): gate and up values alternate in blocks of that many instead of F gates, then F ups.
 FMX_EXPORT int fmx_moe_expert_act(const void* gu, long long gu_stride, const float* weights, void* out, long long out_stride,
-                                  int rows, int E, int ff, int F, float limit, float limit_shared, int dtype,
+                                  int rows, int E, int ff, int F, float limit, float limit_shared, int dtype, int gu_block,
                                   cudaStream_t stream) {
+  if (gu_block < 0 || (gu_block > 0 && (F % gu_block || gu_block % 8))) return fmx_fail("fmx_moe_expert_act: blocks of %d do not fit %d columns", gu_block, F);
   if (rows == 0 || F == 0) return 0;
   if (rows < 0 || E < 0 || ff <= 0 || F < E * ff || gu_stride < 2LL * F || out_stride < F)
     return fmx_fail("fmx_moe_expert_act: bad sizes rows=%d E=%d ff=%d F=%d", rows, E, ff, F);
@@ -178,13 +185,13 @@ FMX_EXPORT int fmx_moe_expert_act(const void* gu, long long gu_stride, const flo
   const int grid = (int)((n + block - 1) / block < cap ? (n + block - 1) / block : cap);
   if (vec)
     fmx_launch(moe_expert_act_vec_kernel, dim3(grid), dim3(block), 0, stream, (const bf16*)gu, gu_stride, weights, (bf16*)out,
-               out_stride, (long long)rows, E, ff, F, limit, limit_shared);
+               out_stride, (long long)rows, E, ff, F, limit, limit_shared, gu_block);
   else if (dtype == FMX_F32)
     fmx_launch(moe_expert_act_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gu, gu_stride, weights, (float*)out,
-               out_stride, (long long)rows, E, ff, F, limit, limit_shared);
+               out_stride, (long long)rows, E, ff, F, limit, limit_shared, gu_block);
   else if (dtype == FMX_BF16)
     fmx_launch(moe_expert_act_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gu, gu_stride, weights, (bf16*)out,
-               out_stride, (long long)rows, E, ff, F, limit, limit_shared);
+               out_stride, (long long)rows, E, ff, F, limit, limit_shared, gu_block);
   else
     return fmx_fail("fmx_moe_expert_act: unknown dtype %d", dtype);
   FMX_LAUNCH_CHECK();

@@ -213,7 +213,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int out_n0 = n_tile * OUT_COLS;
       const int n_out = GATED ? N / 2 : N;
       const bool row_in_use = row < M && (gr.row_token == nullptr || gr.row_token[row] >= 0);
-      const float row_w = (EPI == EPI_EXPERT && row_in_use) ? gr.row_weight[row] : 0.f;
+      const float row_w = (EPI == EPI_EXPERT && row_in_use) ? (gr.row_weight != nullptr ? gr.row_weight[row] : 1.0f) : 0.f;
 #pragma unroll 1
       for (int c = 0; c < OUT_COLS; c += 16) {
         uint32_t v[16], u[16];
@@ -312,6 +312,19 @@ int run(const void* A, long long lda, const void* W, long long ldw, void* C, lon
   return 0;
 }
 }  // namespace
+
+// One expert for every row (a shared expert): A [M, K], W [N = 2 ff, K] in blocks of 128 gate rows followed by their 128 up
+// rows, C bfloat16 [M, ff] = g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+FMX_EXPORT int fmx_expert_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int M, int N,
+                                  int K, float limit, int sms, int* status, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (M < 0 || N <= 0 || K <= 0 || N % 256) return fmx_fail("fmx_expert_tcgen05: bad sizes M=%d N=%d K=%d (2 ff a multiple of 256)", M, N, K);
+  if (K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
+    return fmx_fail("fmx_expert_tcgen05: rows must start on 16-byte boundaries (K=%d lda=%lld ldw=%lld)", K, lda, ldw);
+  if (sms <= 0) sms = fmx_num_sms();
+  const Grouped gr{nullptr, nullptr, nullptr, nullptr, 0, limit};
+  return run<256, EPI_EXPERT>(A, lda, W, ldw, C, ldc, nullptr, 0, M, N, K, sms, status, stream, gr, 0);
+}
 
 // A routed feed-forward's products over sorted pairs (see `Grouped`).  A [max_rows, K] bfloat16: the pairs' inputs in sorted
 // order, max_rows a multiple of 128.  W: `experts` matrices of N rows each, one under the other, K-contiguous.

@@ -574,10 +574,11 @@ def moe_route(logits, top: int, groups: int = 1, keep: int = 1, want_chosen: boo
     return (w, chosen) if want_chosen else w
 
 
-def moe_expert_act(gu, weights, E: int, ff: int, limit: float, limit_shared: float = 0.0, out=None):
+def moe_expert_act(gu, weights, E: int, ff: int, limit: float, limit_shared: float = 0.0, out=None, block: int = 0):
     """The experts' hidden layers side by side: gu[T, 2F] holds F gates then F ups, F = E*ff + the shared expert's
     width; -> [T, F]: w * g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit), w the
-    token's weight for the column's expert (1 for the shared columns at the end), zero where it chose it not."""
+    token's weight for the column's expert (1 for the shared columns at the end), zero where it chose it not.
+    `block` > 0: gu holds gates and ups in alternating blocks of that many instead."""
     _need_cuda(gu, weights)
     assert gu.dim() == 2 and gu.stride(1) == 1 and gu.shape[1] % 2 == 0 and weights.dtype == torch.float32
     T, F = gu.shape[0], gu.shape[1] // 2
@@ -585,7 +586,25 @@ def moe_expert_act(gu, weights, E: int, ff: int, limit: float, limit_shared: flo
     if out is None:
         out = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
     call("common", "fmx_moe_expert_act", gu.data_ptr(), gu.stride(0), weights.data_ptr(), out.data_ptr(), out.stride(0), T,
-         int(E), int(ff), F, float(limit), float(limit_shared), _dt(gu), _stream())
+         int(E), int(ff), F, float(limit), float(limit_shared), _dt(gu), int(block), _stream())
+    return out
+
+
+def can_expert_tc(x, w) -> bool:
+    """Does a shared expert's gate/up product of these sizes go to the tcgen05 kernel with the expert's activation in its
+    epilogue?  As `can_tc` with the SiLU-mul epilogue: bfloat16, at least 128 rows, gate/up rows in blocks of 128, full rounds."""
+    return (_bf16_operands(x, w) and x.shape[0] >= TC_MIN_ROWS and w.shape[0] % (2 * GATE_UP_BLOCK) == 0
+            and tc_fills_the_gpu(x.shape[0], w.shape[0], num_sms(x.device)))
+
+
+def expert_gate_up_tc(x, w, limit: float, status=None) -> torch.Tensor:
+    """g' sigmoid(1.702 g') (u' + 1) of x w^T, g' = min(g, limit), u' = clamp(u, -limit, limit), for w [2 ff, K] in blocks of 128
+    gate rows followed by their up rows: product and activation in one tcgen05 kernel.  -> bfloat16 [M, ff]."""
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    call("tc", "fmx_expert_tcgen05", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K,
+         float(limit), num_sms(x.device), _ptr(status if status is not None else _status_word(x.device)), _stream())
     return out
 
 

@@ -48,7 +48,7 @@ _SIGNATURES = {
         "fmx_rmsnorm_rows": [_P, _L, _I, _P, _F, _P, _L, _I, _P, _L, _I, _I, _P, _P],
         "fmx_sigmoid_gate": [_P, _L, _I, _P, _L, _I, _I, _I, _I, _P],
         "fmx_moe_route": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P],
-        "fmx_moe_expert_act": [_P, _L, _P, _P, _L, _I, _I, _I, _I, _F, _F, _I, _P],
+        "fmx_moe_expert_act": [_P, _L, _P, _P, _L, _I, _I, _I, _I, _F, _F, _I, _I, _P],
     },
     "bf16": {
         "fmx_gemv": [_P, _L, _P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -61,6 +61,7 @@ _SIGNATURES = {
     },
     "tc": {
         "fmx_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],
+        "fmx_expert_tcgen05": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _F, _I, _P, _P],
         "fmx_grouped_tcgen05": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _F, _I, _I, _P, _P],
     },
     "attn": {

@@ -77,8 +77,17 @@ class RoutedExperts(FeedForward):
         n = len(self.gate_names)
         gates, ups, downs = mats[:n], mats[n:2 * n], mats[2 * n:]
         self.shared_gate_up = self.shared_down = None
+        self.shared_block = 0
         if self.sparse and self.shared_ff:        # the shared expert is an ordinary gated feed-forward beside the routed ones
-            self.shared_gate_up = torch.cat([gates.pop(), ups.pop()], 0).contiguous()
+            g, u = gates.pop(), ups.pop()
+            sb = int(getattr(rt.k, "GATE_UP_BLOCK", 0) or 0)
+            if sb and self.shared_ff % sb == 0 and hasattr(rt.k, "expert_gate_up_tc"):
+                # gate and up rows in blocks, as the tcgen05 product's epilogue takes them (the activation rides there)
+                self.shared_block = sb
+                self.shared_gate_up = torch.stack([g.view(-1, sb, self.width), u.view(-1, sb, self.width)], 1) \
+                    .reshape(-1, self.width).contiguous()
+            else:
+                self.shared_gate_up = torch.cat([g, u], 0).contiguous()
             self.shared_down = downs.pop().contiguous()
         # grouped products of wide experts: expert after expert, gate and up rows in alternating blocks (a tile of the
         # tcgen05 product then holds gates and their ups), down matrices one under the other (rows of ff for its TMA)
@@ -130,7 +139,11 @@ class RoutedExperts(FeedForward):
         pairs = k.moe_grouped_down(y, plan, self.down, self.E, self.ff, stacked=bool(self.block), tokens=T)
         shared = None
         if self.shared_gate_up is not None:
-            gu = k.linear(x, self.shared_gate_up, None, self.rt.dtype)
-            none = torch.empty((T, 0), dtype=torch.float32, device=x.device)
-            shared = k.linear(k.moe_expert_act(gu, none, 0, 8, 0.0, self.shared_limit), self.shared_down, None, self.rt.dtype)
+            if self.shared_block and k.can_expert_tc(x, self.shared_gate_up):
+                act = k.expert_gate_up_tc(x, self.shared_gate_up, self.shared_limit)
+            else:
+                gu = k.linear(x, self.shared_gate_up, None, self.rt.dtype)
+                none = torch.empty((T, 0), dtype=torch.float32, device=x.device)
+                act = k.moe_expert_act(gu, none, 0, 8, 0.0, self.shared_limit, block=self.shared_block)
+            shared = k.linear(act, self.shared_down, None, self.rt.dtype)
         return k.moe_combine(pairs, plan, shared, T, self.top, self.rt.dtype)

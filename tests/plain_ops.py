@@ -335,9 +335,13 @@ def moe_route(logits, top, groups=1, keep=1, want_chosen=False):
     return (w, chosen) if want_chosen else w
 
 
-def moe_expert_act(gu, weights, E, ff, limit, limit_shared=0.0, out=None):
+def moe_expert_act(gu, weights, E, ff, limit, limit_shared=0.0, out=None, block=0):
     T, F = gu.shape[0], gu.shape[1] // 2
-    g, u = gu[:, :F].to(F64), gu[:, F:].to(F64)
+    if block:
+        v = gu.reshape(T, F // block, 2, block).to(F64)
+        g, u = v[:, :, 0].reshape(T, F), v[:, :, 1].reshape(T, F)
+    else:
+        g, u = gu[:, :F].to(F64), gu[:, F:].to(F64)
     lim = torch.full((F,), float(limit), dtype=F64)
     lim[E * ff:] = float(limit_shared)
     w = torch.ones(T, F, dtype=F64)

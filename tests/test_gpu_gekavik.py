@@ -304,6 +304,15 @@ def test_expert_activation_and_products_per_head(dtype):
         got = k.moe_expert_act(x.to(DEV), w.to(DEV), E, ff, lim, lim_s)
         assert torch.allclose(got.cpu().double(), want.double(), atol=tol, rtol=tol)
         assert (got.cpu()[:, :E * ff].view(T, E, ff).abs().sum(-1) > 0).eq(w > 0).all()      # zero where not chosen
+    # one expert for all, gates and ups in alternating blocks of 8
+    x = gu[:, :2 * 24].contiguous()
+    none = torch.empty((T, 0))
+    want = plain_ops.moe_expert_act(x, none, 0, 8, 0.0, 1.3, block=8)
+    got = k.moe_expert_act(x.to(DEV), none.to(DEV), 0, 8, 0.0, 1.3, block=8)
+    assert torch.allclose(got.cpu().double(), want.double(), atol=tol, rtol=tol)
+    g_, u_ = x.double().view(T, 3, 2, 8)[:, :, 0].reshape(T, 24), x.double().view(T, 3, 2, 8)[:, :, 1].reshape(T, 24)
+    direct = torch.clamp(g_, max=1.3) * torch.sigmoid(1.702 * torch.clamp(g_, max=1.3)) * (torch.clamp(u_, -1.3, 1.3) + 1)
+    assert torch.allclose(want.double(), direct, atol=tol, rtol=tol)
     H, N, K = 3, 10, 24
     x = torch.randn(T, H * K + 8, generator=g).to(dtype)
     wt = (torch.randn(H, N, K, generator=g) / K ** 0.5).to(dtype)
@@ -314,13 +323,14 @@ def test_expert_activation_and_products_per_head(dtype):
 
 
 @pytest.mark.parametrize("E,top,ff,groups,keep,shared", [(8, 2, 24, 4, 2, 40), (6, 3, 64, 1, 1, 0), (16, 4, 8, 8, 3, 8), (3, 1, 136, 1, 1, 16),
-                                                           (4, 2, 128, 1, 1, 0), (8, 2, 256, 4, 2, 40)])
+                                                           (4, 2, 128, 1, 1, 0), (8, 2, 256, 4, 2, 40), (4, 2, 128, 2, 1, 2560)])
 @pytest.mark.parametrize("T", [1, 5, 70, 333, 700])
 def test_grouped_products_of_the_routed_experts(E, top, ff, groups, keep, shared, T):
     """The path of large experts on small ones: pairs sorted expert by expert on the device, tiles of pairs against
     their expert's matrices, outputs added per token; against the plain feed-forward and against the path that runs
     all experts side by side.  Experts whose width is a multiple of 128 keep their rows in blocks, and steps of 128 tokens
-    and more multiply them on the tcgen05 kernel."""
+    and more multiply them on the tcgen05 kernel; a shared expert wide enough to fill the GPU's rounds takes that kernel too,
+    with its activation in the epilogue."""
     from fastmlx_b200.engine.loading import make_runtime
     from fastmlx_b200.parts import RoutedExperts
     d = 72
